@@ -1,0 +1,147 @@
+"""ctypes/numpy front-end of the CPU oracle (oracle/e8_oracle.c).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by __graft_entry__.smoke() and by bench.py's
+CPU-baseline legs.  Nothing under coset_b200/ may import this module.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "_build", "libe8_oracle.so")
+_lib = None
+
+_f32p = ctypes.POINTER(ctypes.c_float)
+_u32p = ctypes.POINTER(ctypes.c_uint32)
+
+
+def build(force=False):
+    """Compile the C oracle with gcc (oracle/Makefile)."""
+    src = os.path.join(_HERE, "e8_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "-s"])
+    return _SO
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        _lib = ctypes.CDLL(_SO)
+        _lib.e8o_custom_round.restype = ctypes.c_float
+        _lib.e8o_custom_round.argtypes = [ctypes.c_float]
+    return _lib
+
+
+def _f32(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return a, a.ctypes.data_as(_f32p)
+
+
+def generators():
+    g = np.empty((8, 8), np.float32)
+    gi = np.empty((8, 8), np.float32)
+    lib().e8o_generators(g.ctypes.data_as(_f32p), gi.ctypes.data_as(_f32p))
+    return g, gi
+
+
+def custom_round(x):
+    x = np.asarray(x, np.float32)
+    out = np.empty_like(x)
+    L = lib()
+    flat_in, flat_out = x.reshape(-1), out.reshape(-1)
+    for i in range(flat_in.size):
+        flat_out[i] = L.e8o_custom_round(float(flat_in[i]))
+    return out
+
+
+def _rows(fn, x, *extra):
+    x, xp = _f32(x)
+    assert x.shape[-1] == 8
+    out = np.empty_like(x)
+    flat = x.reshape(-1, 8)
+    o = out.reshape(-1, 8)
+    L = lib()
+    f = getattr(L, fn)
+    for i in range(flat.shape[0]):
+        f(flat[i].ctypes.data_as(_f32p), *extra, o[i].ctypes.data_as(_f32p))
+    return out
+
+
+def g_x(x):
+    return _rows("e8o_g_x", x)
+
+
+def projection(x):
+    return _rows("e8o_projection", x)
+
+
+def encode_coords(p, q):
+    return _rows("e8o_encode_coords", p, ctypes.c_int(q))
+
+
+def decode_coords(b):
+    return _rows("e8o_decode_coords", b)
+
+
+def _beta_arg(beta, scale_mode):
+    if scale_mode == 0 or beta is None:
+        b = np.ones(1, np.float32)
+    else:
+        b = np.ascontiguousarray(np.atleast_1d(beta), dtype=np.float32).reshape(-1)
+    return b, b.ctypes.data_as(_f32p)
+
+
+def encode(x, beta=None, scale_mode=0, blocks_per_tile=1, q=4, M=2, threads=1):
+    """-> float32 digits [n, M, 8], exactly what the reference's e8_encode returns."""
+    x, xp = _f32(x)
+    n = x.shape[0]
+    b, bp = _beta_arg(beta, scale_mode)
+    codes = np.empty((n, M, 8), np.float32)
+    lib().e8o_encode_mt(xp, ctypes.c_int64(n), bp, scale_mode, ctypes.c_int64(blocks_per_tile), q, M,
+                        codes.ctypes.data_as(_f32p), threads)
+    return codes
+
+
+def decode(codes, beta=None, scale_mode=0, blocks_per_tile=1, q=4, threads=1):
+    codes, cp = _f32(codes)
+    n, M, _ = codes.shape
+    b, bp = _beta_arg(beta, scale_mode)
+    out = np.empty((n, 8), np.float32)
+    lib().e8o_decode_mt(cp, ctypes.c_int64(n), bp, scale_mode, ctypes.c_int64(blocks_per_tile), q, M,
+                        out.ctypes.data_as(_f32p), threads)
+    return out
+
+
+def quantize(x, q=4):
+    x, xp = _f32(x)
+    out = np.empty_like(x)
+    lib().e8o_quantize(xp, ctypes.c_int64(x.shape[0]), q, out.ctypes.data_as(_f32p))
+    return out
+
+
+def fake_quant(w_blocks, beta, blocks_per_tile, q=4, clip=2.0):
+    """-> (clamped, unclipped) float32 [n, 8]."""
+    w, wp = _f32(w_blocks)
+    b, bp = _beta_arg(beta, 2)
+    wq = np.empty_like(w)
+    un = np.empty_like(w)
+    lib().e8o_fake_quant(wp, ctypes.c_int64(w.shape[0]), bp, ctypes.c_int64(blocks_per_tile), q,
+                         ctypes.c_float(clip), wq.ctypes.data_as(_f32p), un.ctypes.data_as(_f32p))
+    return wq, un
+
+
+def pack_q4(codes):
+    """float digits [n, M<=2, 8] -> uint32 [n] in the CUDA library's packed layout."""
+    codes, cp = _f32(codes)
+    n, M, _ = codes.shape
+    out = np.empty(n, np.uint32)
+    lib().e8o_pack_q4(cp, ctypes.c_int64(n), M, out.ctypes.data_as(_u32p))
+    return out
+
+
+def codes_to_int(codes):
+    """Reference digits are float32 and may be -0.0; compare them as integers."""
+    return np.asarray(codes).astype(np.int64)
