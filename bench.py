@@ -1,0 +1,369 @@
+#!/usr/bin/env python
+"""Headline benchmark: bulk E8 HNLQ codec throughput (encode + decode GB/s, fraction of HBM peak).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE config "bulk codec"): float32 [2^25, 8] (2^28 values), N(0, 0.02) with 0.1 %
+of the entries replaced by +-10 sigma outliers, clipped to +-2, q=4, M=2, one float32 scale per
+8-value block in the layer (multiply) convention.  One STEP = one encode pass (x -> packed
+codes) followed by one decode pass (codes -> x_hat) over the whole batch.  Algorithmic bytes per
+block: encode 32 + 4 + 4, decode 4 + 4 + 32 => 80 B per block per step.
+
+The literal scale of that config (beta at theta=0 = 0.02144) maps every block to the all-zero
+code, so the headline uses beta = 25 (scaled sigma 0.5: every branch of the search is exercised,
+about half the blocks take the parity flip and ~45 % the half-integer coset); the literal scale
+is reported next to it under "detail".
+
+Multi-GPU (--gpus N under torch.distributed.run): blocks are independent, each rank runs the
+same per-GPU workload on its own seed (weak scaling, no data-path collective); the time is the
+max over ranks.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_BLOCKS = 1 << 25
+BYTES_PER_BLOCK_ENC = 40
+BYTES_PER_BLOCK_DEC = 40
+BYTES_PER_BLOCK_STEP = BYTES_PER_BLOCK_ENC + BYTES_PER_BLOCK_DEC
+BETA_HEADLINE = 25.0
+BETA_LITERAL = 0.021440971642732620
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one encode launch, from the ncu capture
+# summarised in profiles/ (null until a capture exists for the current kernel).
+ENCODE_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def make_values(n_values, seed):
+    """The config's synthetic distribution, generated in fixed chunks of 2^24 values."""
+    g = torch.Generator().manual_seed(seed)
+    out = torch.empty(n_values, dtype=torch.float32)
+    chunk = 1 << 24
+    for lo in range(0, n_values, chunk):
+        n = min(chunk, n_values - lo)
+        v = torch.randn(n, generator=g) * 0.02
+        m = torch.rand(n, generator=g) < 1e-3
+        s = torch.randint(0, 2, (n,), generator=g) * 2 - 1
+        v[m] = 0.2 * s[m].float()
+        out[lo:lo + n] = v.clamp_(-2.0, 2.0)
+    return out
+
+
+def hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback (earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons during the timed region."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [t.strip() for t in line.split(",")]
+                if len(f) < 7:
+                    continue
+                try:
+                    sm.append(float(f[0])); mx.append(float(f[1]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, f[3:7]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if not sm:
+            return None
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def time_kernels(fn_list, steps, warmup):
+    """Runs the kernels of one step in order, `steps` times; returns (total ms, per-kernel mean ms)."""
+    for _ in range(warmup):
+        for fn in fn_list:
+            fn()
+    torch.cuda.synchronize()
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(len(fn_list) + 1)] for _ in range(steps)]
+    for s in range(steps):
+        marks[s][0].record()
+        for i, fn in enumerate(fn_list):
+            fn()
+            marks[s][i + 1].record()
+    torch.cuda.synchronize()
+    total = marks[0][0].elapsed_time(marks[-1][-1])
+    per = [sum(m[i].elapsed_time(m[i + 1]) for m in marks) / steps for i in range(len(fn_list))]
+    return total, per
+
+
+def cpu_port_throughput(x_cpu, beta_cpu, sample_blocks, threads, repeats=1):
+    """The CPU oracle (C restatement of the reference) on a prefix of the workload, all host cores."""
+    from oracle import oracle as O
+    xs = x_cpu[:sample_blocks].numpy()
+    bs = beta_cpu[:sample_blocks].numpy()
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        codes = O.encode(xs, beta=bs, scale_mode=2, blocks_per_tile=1, q=4, M=2, threads=threads)
+        O.decode(codes, beta=bs, scale_mode=2, blocks_per_tile=1, q=4, threads=threads)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return sample_blocks * BYTES_PER_BLOCK_STEP / best / 1e9, best
+
+
+def base_line(args, world):
+    return {
+        "metric": "E8 HNLQ encode+decode GB/s (% HBM peak)",
+        "unit": "GB/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "f32",
+        "data": "synthetic (seeded N(0,0.02) + 0.1% +-10sigma outliers, clip 2.0)",
+        "config": {
+            "workload": "bulk E8 HNLQ codec: fp32 [2^25, 8] per GPU, q=4, M=2, per-block scale beta=25 "
+                        "(layer/multiply convention); step = encode pass + decode pass, 80 B/block",
+            "n_blocks_per_gpu": N_BLOCKS,
+            "q": 4, "M": 2, "beta": BETA_HEADLINE,
+            "l2": "inputs (1 GiB per pass) larger than L2, no flush needed",
+        },
+    }
+
+
+def run_reference(args, rank, world):
+    """The reference's CPU path (C port of coset.core.e8, all host threads) on a bounded sample."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    sample = 1 << 21
+    x = make_values(sample * 8, 0).view(sample, 8)
+    beta = torch.full((sample,), BETA_HEADLINE)
+    for _ in range(args.warmup):
+        cpu_port_throughput(x, beta, sample, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_port_throughput(x, beta, sample, threads)
+    dt = time.perf_counter() - t0
+    value = args.steps * sample * BYTES_PER_BLOCK_STEP / dt / 1e9
+    line = base_line(args, world)
+    line.update({
+        "impl": "reference", "value": value, "ms_per_step": dt / args.steps * 1e3, "gpu_launches": 0,
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"first {sample} blocks of the workload per step (1/16 of a GPU step)"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    })
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--blocks", type=int, default=N_BLOCKS, help="blocks per GPU (default: the config's 2^25)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-detail", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch.distributed as dist
+    from coset_b200 import _lib
+    from coset_b200.core.e8 import e8_decode_packed, e8_encode_packed
+    from coset_b200.core.e8.codecs import _lib as _  # noqa: F401  (fails loudly if the CUDA library is missing)
+
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    n = args.blocks
+    x_cpu = make_values(n * 8, rank).view(n, 8)
+    beta_cpu = torch.full((n,), BETA_HEADLINE)
+    x = x_cpu.cuda()
+    beta = beta_cpu.cuda()
+    codes = torch.empty((n, 4), dtype=torch.uint8, device="cuda")
+    xhat = torch.empty((n, 8), dtype=torch.float32, device="cuda")
+    MT = _lib.SCALE_MUL_TILE
+
+    def enc():
+        e8_encode_packed(x, 4, 2, scale=beta, scale_mode=MT, blocks_per_tile=1, out=codes)
+
+    def dec():
+        e8_decode_packed(codes, 4, 2, scale=beta, scale_mode=MT, blocks_per_tile=1, out=xhat)
+
+    # ---- timed region: K steps of (encode, decode), inputs resident in HBM
+    for _ in range(args.warmup):
+        enc(); dec()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    torch.cuda.synchronize()
+    total_ms, per = time_kernels([enc, dec], args.steps, 0)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop() if sampler else None
+    t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    value = world * args.steps * n * BYTES_PER_BLOCK_STEP / (total_ms * 1e-3) / 1e9
+
+    # ---- end to end through the host-buffer API (pinned host arrays in, host arrays out)
+    e2e = None
+    if not args.no_e2e:
+        from coset_b200.host import HostCodec
+        hc = HostCodec(chunk_blocks=1 << 21, n_slots=4)
+        xh = x_cpu.pin_memory()
+        bh = beta_cpu.pin_memory()
+        ch = torch.empty((n, 4), dtype=torch.uint8, pin_memory=True)
+        oh = torch.empty((n, 8), dtype=torch.float32, pin_memory=True)
+        e2e_steps = max(3, min(args.steps, 10))
+        for _ in range(2):
+            hc.encode(xh, scale=bh, scale_mode=MT, out=ch); hc.decode(ch, scale=bh, scale_mode=MT, out=oh)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            hc.encode(xh, scale=bh, scale_mode=MT, out=ch)
+            hc.decode(ch, scale=bh, scale_mode=MT, out=oh)
+        torch.cuda.synchronize()
+        dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        e2e = {"value": world * e2e_steps * n * BYTES_PER_BLOCK_STEP / float(dt.item()) / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": n * (32 + 4 + 4 + 4), "d2h_bytes_per_step": n * (4 + 32), "steps": e2e_steps,
+               "api": "coset_b200.host.HostCodec.encode/.decode -> coset_e8_encode_host / coset_e8_decode_host"}
+        ok = torch.equal(oh[:4096], xhat[:4096].cpu())
+        e2e["matches_device_path"] = bool(ok)
+        hc.close()
+        del xh, ch, oh
+
+    # ---- detail: each kernel alone, the fused round trip, bf16, and the literal (degenerate) scale
+    detail = {}
+    if not args.no_detail and rank == 0:
+        from coset_b200 import _lib as L
+        k = max(5, min(args.steps, 20))
+
+        def gbs(ms, bytes_per_block):
+            return n * bytes_per_block / (ms * 1e-3) / 1e9
+
+        _, p = time_kernels([enc], k, 3); detail["encode_f32_GBps"] = gbs(p[0], 40)
+        _, p = time_kernels([dec], k, 3); detail["decode_f32_GBps"] = gbs(p[0], 40)
+        out = torch.empty_like(x)
+
+        def rt():
+            rc = L.lib().coset_e8_quantize(L.ptr(x), 0, L.ptr(beta), MT, n, 1, 4, 2, 0.0, L.ptr(out), 0, None, L.stream())
+            L.check(rc, "coset_e8_quantize")
+        _, p = time_kernels([rt], k, 3); detail["roundtrip_f32_GBps"] = gbs(p[0], 68)
+        del out
+        xb = x.to(torch.bfloat16)
+        ob = torch.empty_like(xb)
+
+        def encb():
+            e8_encode_packed(xb, 4, 2, scale=beta, scale_mode=MT, blocks_per_tile=1, out=codes)
+
+        def decb():
+            e8_decode_packed(codes, 4, 2, scale=beta, scale_mode=MT, blocks_per_tile=1, out=ob)
+        _, p = time_kernels([encb, decb], k, 3)
+        detail["encode_bf16_GBps"] = gbs(p[0], 24); detail["decode_bf16_GBps"] = gbs(p[1], 24)
+        del xb, ob
+        beta_lit = torch.full((n,), BETA_LITERAL, device="cuda")
+
+        def encl():
+            e8_encode_packed(x, 4, 2, scale=beta_lit, scale_mode=MT, blocks_per_tile=1, out=codes)
+
+        def decl():
+            e8_decode_packed(codes, 4, 2, scale=beta_lit, scale_mode=MT, blocks_per_tile=1, out=xhat)
+        tl, p = time_kernels([encl, decl], k, 3)
+        detail["literal_beta_theta0"] = {"beta": BETA_LITERAL, "encode_GBps": gbs(p[0], 40), "decode_GBps": gbs(p[1], 40),
+                                         "encode+decode_GBps": gbs(p[0] + p[1], 80), "note": "all codes are zero at this scale"}
+        enc(); dec()  # restore headline buffers
+
+    # ---- CPU baseline (rank 0, single-GPU run only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        sample = min(n, 1 << 22)
+        v, secs = cpu_port_throughput(x_cpu, beta_cpu, sample, threads)
+        cpu = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
+               "sample": f"first {sample} of {n} blocks, one encode+decode pass, {secs:.2f} s"}
+
+    if rank == 0:
+        peak, peak_src = hbm_peak()
+        enc_ms = per[0]
+        achieved = n * BYTES_PER_BLOCK_ENC / (enc_ms * 1e-3) / 1e9
+        line = base_line(args, world)
+        line["config"]["n_blocks_per_gpu"] = n
+        line.update({
+            "value": value,
+            "ms_per_step": total_ms / args.steps,
+            "gpu_launches": 2 * args.steps,
+            "frac_of_hbm_peak": value / world / peak,
+            "roofline": {"bound": "hbm", "kernel": "k_encode_q4m2 (dominant: %.0f%% of the step)" % (100 * per[0] / (per[0] + per[1])),
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": ENCODE_TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes_per_launch": n * BYTES_PER_BLOCK_ENC,
+                         "peak_source": peak_src, "ms_per_launch": enc_ms,
+                         "decode": {"achieved": n * BYTES_PER_BLOCK_DEC / (per[1] * 1e-3) / 1e9, "ms_per_launch": per[1]}},
+            "clocks": clocks,
+            "e2e": e2e,
+            "cpu_baseline": cpu,
+            "detail": detail,
+        })
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

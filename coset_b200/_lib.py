@@ -1,0 +1,85 @@
+"""ctypes binding of libcoset_b200.so, the C-ABI CUDA library.
+
+There is no CPU fallback: if the library is missing or a tensor is not on a CUDA device the
+call fails loudly.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libcoset_b200.so")
+
+DTYPE_F32, DTYPE_BF16 = 0, 1
+SCALE_NONE, SCALE_DIV_SCALAR, SCALE_MUL_TILE = 0, 1, 2
+SEM_CORE, SEM_REF = 0, 1
+
+_lib = None
+
+_vp, _i64, _i32, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
+
+# name -> argtypes; every symbol declared in include/coset_b200.h
+SIGNATURES = {
+    "coset_version": [],
+    "coset_last_error_string": [],
+    "coset_e8_code_bytes": [_i32, _i32],
+    "coset_e8_projection": [_vp, _i64, _vp, _vp],
+    "coset_e8_encode": [_vp, _i32, _vp, _i32, _i64, _i64, _i32, _i32, _i32, _vp, _vp],
+    "coset_e8_decode": [_vp, _vp, _i32, _i64, _i64, _i32, _i32, _i32, _vp, _i32, _vp],
+    "coset_e8_quantize": [_vp, _i32, _vp, _i32, _i64, _i64, _i32, _i32, _f32, _vp, _i32, _vp, _vp],
+    "coset_e8_unpack_codes_f32": [_vp, _i64, _i32, _i32, _vp, _vp],
+    "coset_e8_pack_codes_f32": [_vp, _i64, _i32, _i32, _vp, _vp],
+    "coset_host_ctx_create": [_i64, _i32, ctypes.POINTER(ctypes.c_void_p)],
+    "coset_host_ctx_destroy": [_vp],
+    "coset_e8_encode_host": [_vp, _vp, _i32, _vp, _i32, _i64, _i64, _i32, _i32, _vp],
+    "coset_e8_decode_host": [_vp, _vp, _vp, _i32, _i64, _i64, _i32, _i32, _vp, _i32],
+    "coset_e8_fake_quant_bwd": [_vp, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _vp, _vp],
+}
+
+
+def lib():
+    """Loads the shared library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m coset_b200.build` "
+                "(coset_b200 has no CPU or PyTorch fallback)")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.argtypes = argtypes
+            fn.restype = ctypes.c_char_p if name == "coset_last_error_string" else ctypes.c_int
+        _lib = L
+    return _lib
+
+
+def check(rc, what):
+    if rc != 0:
+        msg = lib().coset_last_error_string().decode("utf-8", "replace")
+        raise RuntimeError(f"{what} failed with status {rc}: {msg}")
+
+
+def require_cuda(t, name):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must live on a CUDA device (coset_b200 has no CPU path); got {t.device}")
+    return t
+
+
+def dtype_code(t, name):
+    if t.dtype == torch.float32:
+        return DTYPE_F32
+    if t.dtype == torch.bfloat16:
+        return DTYPE_BF16
+    raise TypeError(f"{name} must be float32 or bfloat16, got {t.dtype}")
+
+
+def ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() > 0 else ctypes.c_void_p(0)
+
+
+def stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)

@@ -1,0 +1,443 @@
+// E8 HNLQ codec kernels and their C-ABI entry points: projection, encode, decode, fused
+// round trip (quantise), packed <-> float32 digit views, and the q=4 residual table.
+//
+// One thread owns one 8-vector ("block"): 32 B in (two 128-bit loads, a warp reads 1 KiB
+// contiguously), all state in registers, 4 B packed code out.  The kernels are HBM-bound by
+// design; algorithmic bytes per block (q=4, M=2, float32): encode 32+4 (+4 per-block scale),
+// decode 4+32 (+4), round trip 32+32 (+4).
+#include <stdarg.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "e8_fast.cuh"
+#include "e8_io.cuh"
+#include "e8_literal.cuh"
+
+namespace coset {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+int check_cuda(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return 0;
+    return fail((int)e, "%s: %s", what, cudaGetErrorString(e));
+}
+int check_launch(const char* what) { return check_cuda(cudaGetLastError(), what); }
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+}  // namespace coset
+
+using namespace coset;
+
+namespace {
+
+constexpr int kThreads = 256;
+
+template <int MODE>
+__device__ __forceinline__ float scale_in(float v, float s) {
+    if (MODE == COSET_SCALE_DIV_SCALAR) return __fdiv_rn(v, s);
+    if (MODE == COSET_SCALE_MUL_TILE) return __fmul_rn(v, s);
+    return v;
+}
+template <int MODE>
+__device__ __forceinline__ float scale_out(float v, float s) {
+    if (MODE == COSET_SCALE_DIV_SCALAR) return __fmul_rn(v, s);
+    if (MODE == COSET_SCALE_MUL_TILE) return __fdiv_rn(v, s);
+    return v;
+}
+template <int MODE>
+__device__ __forceinline__ float load_scale(const float* scale, const e8::TileDiv& td, int64_t block) {
+    if (MODE == COSET_SCALE_DIV_SCALAR) return __ldg(scale);
+    if (MODE == COSET_SCALE_MUL_TILE) return __ldg(scale + e8::tile_of(td, block));
+    return 1.0f;
+}
+
+__device__ __forceinline__ float clampf(float v, float clip) {
+    // torch.clamp: NaN stays NaN
+    if (clip > 0.0f) v = (v < -clip) ? -clip : ((v > clip) ? clip : v);
+    return v;
+}
+
+// ---------------------------------------------------------------- projection
+__global__ void __launch_bounds__(kThreads) k_projection(const float* __restrict__ x, int64_t n, float* __restrict__ y) {
+    int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (b >= n) return;
+    float v[8], o[8];
+    e8::Row8<0>::load(x, b, v);
+    e8::projection(v, o);
+    e8::Row8<0>::store(y, b, o);
+}
+
+// ---------------------------------------------------------------- generic (any 2<=q<=16, M<=8)
+// e8_encode, coset/core/e8/codecs.py:63-83: x_l starts as the scaled input and is divided by q
+// after every level (cumulative IEEE divisions, no re-quantisation).
+template <int BPD>
+__device__ __forceinline__ void encode_levels_generic(float (&xl)[8], int q, int M, uint32_t* words) {
+    float qf = (float)q;
+    for (int m = 0; m < M; ++m) {
+        float y[8];
+        int d[8];
+        bool half = e8::projection(xl, y);
+        e8::encode_coords(y, half, q, d);
+        words[m] = e8::pack_level<BPD>(d);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xl[i] = __fdiv_rn(xl[i], qf);
+    }
+}
+
+// E8Decoder._full_decode, coset/core/e8/codecs.py:159-172 (before the final scale).
+template <int BPD>
+__device__ __forceinline__ void decode_levels_generic(const uint32_t* words, int q, int M, float (&xh)[8]) {
+    float qf = (float)q, w = 1.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) xh[i] = 0.0f;
+    for (int m = 0; m < M; ++m) {
+        int d[8];
+        float r[8];
+        e8::unpack_level<BPD>(words[m], d);
+        e8::level_residual(d, qf, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xh[i] = __fadd_rn(xh[i], __fmul_rn(w, r[i]));
+        w = __fmul_rn(w, qf);
+    }
+}
+
+template <int BPD>
+struct LevelWord;
+template <>
+struct LevelWord<2> { typedef uint16_t type; };
+template <>
+struct LevelWord<4> { typedef uint32_t type; };
+
+template <int DT, int MODE, int BPD>
+__global__ void __launch_bounds__(kThreads)
+k_encode_generic(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n, int q,
+                 int M, void* __restrict__ codes) {
+    int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (b >= n) return;
+    float v[8];
+    e8::Row8<DT>::load(x, b, v);
+    float s = load_scale<MODE>(scale, td, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = scale_in<MODE>(v[i], s);
+    uint32_t words[8];
+    encode_levels_generic<BPD>(v, q, M, words);
+    typename LevelWord<BPD>::type* out = reinterpret_cast<typename LevelWord<BPD>::type*>(codes) + b * M;
+    for (int m = 0; m < M; ++m) out[m] = (typename LevelWord<BPD>::type)words[m];
+}
+
+template <int DT, int MODE, int BPD>
+__global__ void __launch_bounds__(kThreads)
+k_decode_generic(const void* __restrict__ codes, const float* __restrict__ scale, e8::TileDiv td, int64_t n, int q,
+                 int M, void* __restrict__ out) {
+    int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (b >= n) return;
+    const typename LevelWord<BPD>::type* in = reinterpret_cast<const typename LevelWord<BPD>::type*>(codes) + b * M;
+    uint32_t words[8];
+    for (int m = 0; m < M; ++m) words[m] = in[m];
+    float xh[8];
+    decode_levels_generic<BPD>(words, q, M, xh);
+    float s = load_scale<MODE>(scale, td, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) xh[i] = scale_out<MODE>(xh[i], s);
+    e8::Row8<DT>::store(out, b, xh);
+}
+
+template <int DTI, int DTO, int MODE, int BPD>
+__global__ void __launch_bounds__(kThreads)
+k_quantize_generic(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n, int q,
+                   int M, float clip, void* __restrict__ out, void* __restrict__ codes) {
+    int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (b >= n) return;
+    float v[8];
+    e8::Row8<DTI>::load(x, b, v);
+    float s = load_scale<MODE>(scale, td, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = scale_in<MODE>(v[i], s);
+    uint32_t words[8];
+    encode_levels_generic<BPD>(v, q, M, words);
+    if (codes) {
+        typename LevelWord<BPD>::type* co = reinterpret_cast<typename LevelWord<BPD>::type*>(codes) + b * M;
+        for (int m = 0; m < M; ++m) co[m] = (typename LevelWord<BPD>::type)words[m];
+    }
+    float xh[8];
+    decode_levels_generic<BPD>(words, q, M, xh);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) xh[i] = clampf(scale_out<MODE>(xh[i], s), clip);
+    e8::Row8<DTO>::store(out, b, xh);
+}
+
+// ---------------------------------------------------------------- q = 4, M = 2 (one uint32 per block)
+template <int DT, int MODE>
+__global__ void __launch_bounds__(kThreads)
+k_encode_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
+              uint32_t* __restrict__ codes) {
+    int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (b >= n) return;
+    float v[8];
+    e8::Row8<DT>::load(x, b, v);
+    float s = load_scale<MODE>(scale, td, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = scale_in<MODE>(v[i], s);
+    codes[b] = e8::encode_q4m2(v);
+}
+
+template <int DT, int MODE>
+__global__ void __launch_bounds__(kThreads)
+k_decode_q4m2(const uint32_t* __restrict__ codes, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
+              const uint2* __restrict__ table, void* __restrict__ out) {
+    int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (b >= n) return;
+    uint32_t code = __ldg(codes + b);
+    float xh[8];
+    e8::decode_q4m2(code, table, xh);
+    float s = load_scale<MODE>(scale, td, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) xh[i] = scale_out<MODE>(xh[i], s);
+    e8::Row8<DT>::store(out, b, xh);
+}
+
+template <int DTI, int DTO, int MODE>
+__global__ void __launch_bounds__(kThreads)
+k_quantize_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n, float clip,
+                const uint2* __restrict__ table, void* __restrict__ out, uint32_t* __restrict__ codes) {
+    int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (b >= n) return;
+    float v[8];
+    e8::Row8<DTI>::load(x, b, v);
+    float s = load_scale<MODE>(scale, td, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = scale_in<MODE>(v[i], s);
+    uint32_t code = e8::encode_q4m2(v);
+    if (codes) codes[b] = code;
+    float xh[8];
+    e8::decode_q4m2(code, table, xh);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) xh[i] = clampf(scale_out<MODE>(xh[i], s), clip);
+    e8::Row8<DTO>::store(out, b, xh);
+}
+
+// Residual table of the q=4 decoder, produced by the literal float32 decoder itself:
+// entry[w] = 2 * (G b - 4 Q(G b / 4)) for the 16-bit level word w, as 8 int8.
+__global__ void k_build_table_q4(uint2* __restrict__ table) {
+    int w = blockIdx.x * blockDim.x + threadIdx.x;
+    if (w >= 65536) return;
+    int d[8];
+    float r[8];
+    e8::unpack_level<2>((uint32_t)w, d);
+    e8::level_residual(d, 4.0f, r);
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        lo |= ((uint32_t)(__float2int_rn(__fmul_rn(r[i], 2.0f)) & 0xff)) << (8 * i);
+        hi |= ((uint32_t)(__float2int_rn(__fmul_rn(r[i + 4], 2.0f)) & 0xff)) << (8 * i);
+    }
+    table[w] = make_uint2(lo, hi);
+}
+
+// ---------------------------------------------------------------- digit views
+template <int BPD>
+__global__ void __launch_bounds__(kThreads)
+k_unpack_f32(const void* __restrict__ codes, int64_t n_words, float* __restrict__ digits) {
+    int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;  // one level word per thread
+    if (i >= n_words) return;
+    uint32_t w = reinterpret_cast<const typename LevelWord<BPD>::type*>(codes)[i];
+    int d[8];
+    float f[8];
+    e8::unpack_level<BPD>(w, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = (float)d[j];
+    e8::Row8<0>::store(digits, i, f);
+}
+
+template <int BPD>
+__global__ void __launch_bounds__(kThreads)
+k_pack_f32(const float* __restrict__ digits, int64_t n_words, int q, void* __restrict__ codes) {
+    int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= n_words) return;
+    float f[8];
+    int d[8];
+    e8::Row8<0>::load(digits, i, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) d[j] = e8::floored_mod(__float2int_rn(f[j]), q);
+    reinterpret_cast<typename LevelWord<BPD>::type*>(codes)[i] = (typename LevelWord<BPD>::type)e8::pack_level<BPD>(d);
+}
+
+inline unsigned grid_for(int64_t n) { return (unsigned)((n + kThreads - 1) / kThreads); }
+
+int check_common(const void* a, const void* b, int64_t n_blocks, int q, int M) {
+    if (n_blocks < 0) return fail(COSET_E_BADARG, "n_blocks is negative");
+    if (n_blocks > 0 && (!a || !b)) return fail(COSET_E_BADARG, "null data pointer");
+    if (q < 2 || q > 16 || M < 1 || M > 8) return fail(COSET_E_UNSUPPORTED, "unsupported q=%d M=%d (need 2<=q<=16, 1<=M<=8)", q, M);
+    if ((int64_t)grid_for(n_blocks) != (n_blocks + kThreads - 1) / kThreads || n_blocks > ((int64_t)1 << 38))
+        return fail(COSET_E_BADARG, "n_blocks too large");
+    return 0;
+}
+int check_scale(const float* scale, int mode, int64_t bpt) {
+    if (mode < 0 || mode > 2) return fail(COSET_E_BADARG, "unknown scale_mode %d", mode);
+    if (mode != COSET_SCALE_NONE && !scale) return fail(COSET_E_BADARG, "scale is null");
+    if (mode == COSET_SCALE_MUL_TILE && bpt < 1) return fail(COSET_E_BADARG, "blocks_per_tile must be >= 1");
+    return 0;
+}
+
+}  // namespace
+
+namespace coset {
+
+const uint2* residual_table_q4(cudaStream_t stream) {
+    static std::mutex mu;
+    static uint2* tables[64] = {nullptr};
+    int dev = 0;
+    if (check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return nullptr;
+    if (dev < 0 || dev >= 64) { fail(COSET_E_STATE, "device index %d out of range", dev); return nullptr; }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!tables[dev]) {
+        uint2* t = nullptr;
+        if (check_cuda(cudaMalloc(&t, 65536 * sizeof(uint2)), "cudaMalloc(residual table)")) return nullptr;
+        // Built on the caller's stream: every later use on any stream must see it complete, so
+        // the one-time build synchronises that stream.
+        k_build_table_q4<<<65536 / 256, 256, 0, stream>>>(t);
+        if (check_launch("k_build_table_q4") || check_cuda(cudaStreamSynchronize(stream), "table build")) {
+            cudaFree(t);
+            return nullptr;
+        }
+        tables[dev] = t;
+    }
+    return tables[dev];
+}
+
+}  // namespace coset
+
+#define DISPATCH_MODE(MODE_VAR, ...)                                   \
+    switch (MODE_VAR) {                                                \
+        case 0: { constexpr int MODE = 0; __VA_ARGS__; } break;         \
+        case 1: { constexpr int MODE = 1; __VA_ARGS__; } break;         \
+        default: { constexpr int MODE = 2; __VA_ARGS__; } break;        \
+    }
+#define DISPATCH_DT(DT_VAR, NAME, ...)                                 \
+    if ((DT_VAR) == COSET_DTYPE_F32) { constexpr int NAME = 0; __VA_ARGS__; } else { constexpr int NAME = 1; __VA_ARGS__; }
+
+extern "C" {
+
+int coset_version(void) { return 100; }
+const char* coset_last_error_string(void) { return coset::g_err; }
+
+int coset_e8_code_bytes(int q, int M) {
+    if (q < 2 || q > 16 || M < 1 || M > 8) return 0;
+    return M * (q <= 4 ? 2 : 4);
+}
+
+int coset_e8_projection(const float* x, int64_t n_blocks, float* y, void* stream) {
+    if (int e = check_common(x, y, n_blocks, 4, 2)) return e;
+    if (n_blocks == 0) return 0;
+    if (!aligned(x, 16) || !aligned(y, 16)) return fail(COSET_E_ALIGN, "x and y must be 16-byte aligned");
+    k_projection<<<grid_for(n_blocks), kThreads, 0, (cudaStream_t)stream>>>(x, n_blocks, y);
+    return check_launch("k_projection");
+}
+
+int coset_e8_encode(const void* x, int x_dtype, const float* scale, int scale_mode, int64_t n_blocks,
+                    int64_t blocks_per_tile, int q, int M, int sem, void* codes, void* stream) {
+    if (int e = check_common(x, codes, n_blocks, q, M)) return e;
+    if (int e = check_scale(scale, scale_mode, blocks_per_tile)) return e;
+    if (x_dtype != COSET_DTYPE_F32 && x_dtype != COSET_DTYPE_BF16) return fail(COSET_E_BADARG, "unknown x_dtype %d", x_dtype);
+    if (sem != COSET_SEM_CORE) return fail(COSET_E_UNSUPPORTED, "semantics %d not available in this entry point", sem);
+    if (n_blocks == 0) return 0;
+    if (!aligned(x, 16) || !aligned(codes, 4)) return fail(COSET_E_ALIGN, "x must be 16-byte and codes 4-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    e8::TileDiv td = e8::make_tile_div(scale_mode == COSET_SCALE_MUL_TILE ? blocks_per_tile : 1, n_blocks);
+    unsigned grid = grid_for(n_blocks);
+    if (q == 4 && M == 2) {
+        DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2<DT, MODE><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes))))
+    } else if (q <= 4) {
+        DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_generic<DT, MODE, 2><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, q, M, codes))))
+    } else {
+        DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_generic<DT, MODE, 4><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, q, M, codes))))
+    }
+    return check_launch("e8_encode");
+}
+
+int coset_e8_decode(const void* codes, const float* scale, int scale_mode, int64_t n_blocks, int64_t blocks_per_tile,
+                    int q, int M, int sem, void* out, int out_dtype, void* stream) {
+    if (int e = check_common(codes, out, n_blocks, q, M)) return e;
+    if (int e = check_scale(scale, scale_mode, blocks_per_tile)) return e;
+    if (out_dtype != COSET_DTYPE_F32 && out_dtype != COSET_DTYPE_BF16) return fail(COSET_E_BADARG, "unknown out_dtype %d", out_dtype);
+    if (sem != COSET_SEM_CORE) return fail(COSET_E_UNSUPPORTED, "semantics %d not available in this entry point", sem);
+    if (n_blocks == 0) return 0;
+    if (!aligned(out, 16) || !aligned(codes, 4)) return fail(COSET_E_ALIGN, "out must be 16-byte and codes 4-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    e8::TileDiv td = e8::make_tile_div(scale_mode == COSET_SCALE_MUL_TILE ? blocks_per_tile : 1, n_blocks);
+    unsigned grid = grid_for(n_blocks);
+    if (q == 4 && M == 2) {
+        const uint2* table = residual_table_q4(st);
+        if (!table) return COSET_E_STATE;
+        DISPATCH_DT(out_dtype, DT, DISPATCH_MODE(scale_mode, (k_decode_q4m2<DT, MODE><<<grid, kThreads, 0, st>>>((const uint32_t*)codes, scale, td, n_blocks, table, out))))
+    } else if (q <= 4) {
+        DISPATCH_DT(out_dtype, DT, DISPATCH_MODE(scale_mode, (k_decode_generic<DT, MODE, 2><<<grid, kThreads, 0, st>>>(codes, scale, td, n_blocks, q, M, out))))
+    } else {
+        DISPATCH_DT(out_dtype, DT, DISPATCH_MODE(scale_mode, (k_decode_generic<DT, MODE, 4><<<grid, kThreads, 0, st>>>(codes, scale, td, n_blocks, q, M, out))))
+    }
+    return check_launch("e8_decode");
+}
+
+int coset_e8_quantize(const void* x, int x_dtype, const float* scale, int scale_mode, int64_t n_blocks,
+                      int64_t blocks_per_tile, int q, int M, float clip, void* out, int out_dtype, void* codes_out,
+                      void* stream) {
+    if (int e = check_common(x, out, n_blocks, q, M)) return e;
+    if (int e = check_scale(scale, scale_mode, blocks_per_tile)) return e;
+    if ((x_dtype != 0 && x_dtype != 1) || (out_dtype != 0 && out_dtype != 1)) return fail(COSET_E_BADARG, "unknown dtype");
+    if (n_blocks == 0) return 0;
+    if (!aligned(x, 16) || !aligned(out, 16) || !aligned(codes_out, 4)) return fail(COSET_E_ALIGN, "x/out must be 16-byte and codes 4-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    e8::TileDiv td = e8::make_tile_div(scale_mode == COSET_SCALE_MUL_TILE ? blocks_per_tile : 1, n_blocks);
+    unsigned grid = grid_for(n_blocks);
+    if (q == 4 && M == 2) {
+        const uint2* table = residual_table_q4(st);
+        if (!table) return COSET_E_STATE;
+        DISPATCH_DT(x_dtype, DTI, DISPATCH_DT(out_dtype, DTO, DISPATCH_MODE(scale_mode, (k_quantize_q4m2<DTI, DTO, MODE><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, clip, table, out, (uint32_t*)codes_out)))))
+    } else if (q <= 4) {
+        DISPATCH_DT(x_dtype, DTI, DISPATCH_DT(out_dtype, DTO, DISPATCH_MODE(scale_mode, (k_quantize_generic<DTI, DTO, MODE, 2><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, q, M, clip, out, codes_out)))))
+    } else {
+        DISPATCH_DT(x_dtype, DTI, DISPATCH_DT(out_dtype, DTO, DISPATCH_MODE(scale_mode, (k_quantize_generic<DTI, DTO, MODE, 4><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, q, M, clip, out, codes_out)))))
+    }
+    return check_launch("e8_quantize");
+}
+
+int coset_e8_unpack_codes_f32(const void* codes, int64_t n_blocks, int q, int M, float* digits, void* stream) {
+    if (int e = check_common(codes, digits, n_blocks, q, M)) return e;
+    if (n_blocks == 0) return 0;
+    if (!aligned(digits, 16)) return fail(COSET_E_ALIGN, "digits must be 16-byte aligned");
+    int64_t nw = n_blocks * M;
+    if (q <= 4) k_unpack_f32<2><<<grid_for(nw), kThreads, 0, (cudaStream_t)stream>>>(codes, nw, digits);
+    else k_unpack_f32<4><<<grid_for(nw), kThreads, 0, (cudaStream_t)stream>>>(codes, nw, digits);
+    return check_launch("e8_unpack_codes_f32");
+}
+
+int coset_e8_pack_codes_f32(const float* digits, int64_t n_blocks, int q, int M, void* codes, void* stream) {
+    if (int e = check_common(digits, codes, n_blocks, q, M)) return e;
+    if (n_blocks == 0) return 0;
+    if (!aligned(digits, 16)) return fail(COSET_E_ALIGN, "digits must be 16-byte aligned");
+    int64_t nw = n_blocks * M;
+    if (q <= 4) k_pack_f32<2><<<grid_for(nw), kThreads, 0, (cudaStream_t)stream>>>(digits, nw, q, codes);
+    else k_pack_f32<4><<<grid_for(nw), kThreads, 0, (cudaStream_t)stream>>>(digits, nw, q, codes);
+    return check_launch("e8_pack_codes_f32");
+}
+
+}  // extern "C"

@@ -1,0 +1,150 @@
+/*
+ * coset_b200 -- C ABI of the B200 (sm_100a) implementation of coset's E8 hierarchical
+ * nested-lattice quantisation (HNLQ) hot path.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its name ends in `_host`.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).  Calls only
+ *     enqueue work; they never synchronise unless documented.
+ *   - Return value: 0 on success, negative = bad argument (COSET_E_*), positive = cudaError_t.
+ *     Nothing throws or aborts across this boundary.  coset_last_error_string() describes the
+ *     last failure of the calling thread.
+ *   - A "block" is one 8-vector (one E8 lattice cell).  `n_blocks` counts blocks.
+ *
+ * Packed code format ("fast format", additive to the reference's float32 digits)
+ *   bits per digit  bpd = 2 if q <= 4 else 4   (2 <= q <= 16)
+ *   level word      8 digits, digit j at bit bpd*j  -> 16 bits (q<=4) or 32 bits
+ *   block code      M consecutive level words, level 0 first, little endian
+ *   For q = 4, M = 2 a block code is exactly one uint32: level m, digit j at bit 16*m + 2*j.
+ *   coset_e8_code_bytes(q, M) gives the bytes per block.
+ *
+ * Scale modes (which IEEE operation is applied, because the reference has two conventions)
+ *   COSET_SCALE_NONE       x is quantised as is
+ *   COSET_SCALE_DIV_SCALAR encode: x / scale[0];  decode: x_hat * scale[0]
+ *                          (codec convention, coset/core/e8/codecs.py:64 and :175)
+ *   COSET_SCALE_MUL_TILE   encode: x * scale[block / blocks_per_tile];  decode: x_hat / scale[...]
+ *                          (layer convention, coset/core/layers.py:431-436 and :453-460;
+ *                           blocks_per_tile = in_features/8 for tiling='row', 1 for 'block')
+ *
+ * Semantics modes
+ *   COSET_SEM_CORE  bit-exact with coset.core.e8 (float32; including its g_x flip rule and its
+ *                   level recurrence without re-quantisation)
+ *   COSET_SEM_REF   bit-exact with ref/hnlq.py (float64, tie dither, re-quantising recurrence,
+ *                   overload loop); parity-only, not a timed path
+ *
+ * Exactness domain of COSET_SEM_CORE: finite inputs with |scaled x| <= 2^20.  Outside it the
+ * call still succeeds and never faults, but the digits are unspecified.
+ */
+#ifndef COSET_B200_H
+#define COSET_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define COSET_DTYPE_F32 0
+#define COSET_DTYPE_BF16 1
+
+#define COSET_SCALE_NONE 0
+#define COSET_SCALE_DIV_SCALAR 1
+#define COSET_SCALE_MUL_TILE 2
+
+#define COSET_SEM_CORE 0
+#define COSET_SEM_REF 1
+
+#define COSET_E_BADARG (-1)   /* null pointer, negative size, unknown enum */
+#define COSET_E_UNSUPPORTED (-2) /* q / M / dtype combination not implemented */
+#define COSET_E_ALIGN (-3)    /* pointer not aligned as documented */
+#define COSET_E_STATE (-4)    /* library state (context / table) unusable */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int coset_version(void);
+/* Message for the last non-zero return on this thread ("" if none). */
+const char* coset_last_error_string(void);
+/* Bytes of packed code per block; 0 if (q, M) is unsupported. */
+int coset_e8_code_bytes(int q, int M);
+
+/*
+ * E8Lattice.projection (coset/core/e8/lattice.py:114-169): the reference's D8 u (D8+1/2)
+ * search with its own tie rules.  x, y: [n_blocks, 8] float32.
+ */
+int coset_e8_projection(const float* x, int64_t n_blocks, float* y, void* stream);
+
+/*
+ * e8_encode (coset/core/e8/codecs.py:17-89): scale, then M levels of
+ * encode_coords(projection(x / q^m)) (coset/core/base.py:134-154), written as packed codes.
+ * x: [n_blocks, 8] of x_dtype (16-byte aligned).  codes: packed, 4-byte aligned.
+ */
+int coset_e8_encode(const void* x, int x_dtype, const float* scale, int scale_mode,
+                    int64_t n_blocks, int64_t blocks_per_tile, int q, int M, int sem,
+                    void* codes, void* stream);
+
+/*
+ * e8_decode / E8Decoder._full_decode (coset/core/e8/codecs.py:139-218):
+ * x_hat = unscale( sum_m q^m * (G b_m - q * projection(G b_m / q)) ).
+ * out: [n_blocks, 8] of out_dtype (16-byte aligned).
+ */
+int coset_e8_decode(const void* codes, const float* scale, int scale_mode, int64_t n_blocks,
+                    int64_t blocks_per_tile, int q, int M, int sem, void* out, int out_dtype,
+                    void* stream);
+
+/*
+ * Fused round trip decode(encode(x)) without storing codes: e8_quantize
+ * (coset/core/e8/codecs.py:221-286) when scale_mode = NONE, M = 2; with COSET_SCALE_MUL_TILE and
+ * clip > 0 it is the weight path of HNLQLinearQAT._quantize_weights
+ * (coset/core/layers.py:429-463): clamp(e8_quantize(W * beta) / beta, -clip, clip).
+ * clip <= 0 disables the clamp.  codes_out may be NULL; if given it receives the packed codes.
+ */
+int coset_e8_quantize(const void* x, int x_dtype, const float* scale, int scale_mode,
+                      int64_t n_blocks, int64_t blocks_per_tile, int q, int M, float clip,
+                      void* out, int out_dtype, void* codes_out, void* stream);
+
+/*
+ * Compatibility views of the packed codes: the reference returns / accepts digits as float32
+ * [n_blocks, M, 8] (coset/core/e8/codecs.py:83; negative zeros are not reproduced).
+ */
+int coset_e8_unpack_codes_f32(const void* codes, int64_t n_blocks, int q, int M, float* digits,
+                              void* stream);
+int coset_e8_pack_codes_f32(const float* digits, int64_t n_blocks, int q, int M, void* codes,
+                            void* stream);
+
+/*
+ * Backward of the fake-quantised weight path of HNLQLinearQAT (straight-through estimator,
+ * coset/core/layers.py:62-95, with torch autograd's rules for the surrounding
+ * mul / div / clamp of coset/core/layers.py:429-463).  M is 2 (e8_quantize hard-wires it).
+ *   grad_out : dL/dWq           [n_blocks, 8] float32 or bf16
+ *   w        : weights          [n_blocks, 8] float32
+ *   codes    : packed codes written by coset_e8_quantize in the forward pass
+ *   beta     : per-tile scale   [ceil(n_blocks / blocks_per_tile)]
+ *   grad_w   : dL/dW            [n_blocks, 8] float32
+ *   grad_beta: dL/dbeta per tile (may be NULL)
+ */
+int coset_e8_fake_quant_bwd(const void* grad_out, int grad_dtype, const float* w, const void* codes,
+                            const float* beta, int64_t n_blocks, int64_t blocks_per_tile, int q,
+                            float clip, float* grad_w, float* grad_beta, void* stream);
+
+/*
+ * Host-buffer variants: the arrays live in HOST memory (page-locked for full overlap); the
+ * library stages them through a context's device slots, chunk by chunk, with copies in both
+ * directions overlapping the kernels.  This is the call a CPU-side caller of the reference's
+ * e8_encode / e8_decode (coset/core/e8/codecs.py:17-89, 185-218) switches to.  The calls return
+ * when the result is complete in host memory.  The context belongs to the device that was
+ * current when it was created; one call at a time per context.
+ *   chunk_blocks : blocks staged per slot (device memory held: n_slots * chunk_blocks * 68 B)
+ */
+typedef struct coset_host_ctx coset_host_ctx;
+int coset_host_ctx_create(int64_t chunk_blocks, int n_slots, coset_host_ctx** out);
+int coset_host_ctx_destroy(coset_host_ctx* ctx);
+int coset_e8_encode_host(coset_host_ctx* ctx, const void* x_host, int x_dtype, const float* scale_host,
+                         int scale_mode, int64_t n_blocks, int64_t blocks_per_tile, int q, int M,
+                         void* codes_host);
+int coset_e8_decode_host(coset_host_ctx* ctx, const void* codes_host, const float* scale_host,
+                         int scale_mode, int64_t n_blocks, int64_t blocks_per_tile, int q, int M,
+                         void* out_host, int out_dtype);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* COSET_B200_H */
