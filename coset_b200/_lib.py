@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libcoset_b200.so")
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
 SCALE_NONE, SCALE_DIV_SCALAR, SCALE_MUL_TILE = 0, 1, 2
-SEM_CORE, SEM_REF = 0, 1
+SEM_CORE, SEM_REF, SEM_CORE_LITERAL = 0, 1, 2
 
 _lib = None
 

@@ -49,12 +49,14 @@ def _scale_args(scale, scale_mode, n_blocks, blocks_per_tile, device):
 
 
 def e8_encode_packed(x: torch.Tensor, q: int = 4, M: int = 2, scale=None, scale_mode: int = _lib.SCALE_NONE,
-                     blocks_per_tile: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     blocks_per_tile: int = 1, out: Optional[torch.Tensor] = None,
+                     literal: bool = False) -> torch.Tensor:
     """x [N, 8] float32/bfloat16 -> packed codes, uint8 tensor [N, code_bytes(q, M)].
 
     For q=4, M=2 the result can be viewed as int32 [N] (`codes.view(torch.int32)`).
     scale_mode: SCALE_DIV_SCALAR divides by one beta (codec convention); SCALE_MUL_TILE
     multiplies block b by scale[b // blocks_per_tile] (layer convention).
+    literal=True forces the op-by-op search for every block (validation of the fast path).
     """
     x2, _ = _as_blocks(x)
     n = x2.shape[0]
@@ -66,7 +68,8 @@ def e8_encode_packed(x: torch.Tensor, q: int = 4, M: int = 2, scale=None, scale_
         raise ValueError("out has the wrong size, layout or device")
     with torch.cuda.device(x2.device):
         rc = _lib.lib().coset_e8_encode(_lib.ptr(x2), _lib.dtype_code(x2, "x"), _lib.ptr(scale_t), mode, n, bpt,
-                                        q, M, _lib.SEM_CORE, _lib.ptr(out), _lib.stream())
+                                        q, M, _lib.SEM_CORE_LITERAL if literal else _lib.SEM_CORE, _lib.ptr(out),
+                                        _lib.stream())
     _lib.check(rc, "coset_e8_encode")
     return out
 

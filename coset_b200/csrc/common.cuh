@@ -18,7 +18,7 @@ int check_cuda(cudaError_t e, const char* what);
 int sm_count();
 
 // Device pointer to the q=4 single-level residual table of the current device:
-// 65536 entries x 8 int8 = twice the residual G b - 4 Q(G b / 4) of level word `b`.
+// 65536 entries x 8 bytes = twice the residual G b - 4 Q(G b / 4) of level word `b`, plus 7.
 // Built once per device by the library's own literal decoder; nullptr on failure (message stored).
 const uint2* residual_table_q4(cudaStream_t stream);
 

@@ -186,7 +186,7 @@ k_quantize_generic(const void* __restrict__ x, const float* __restrict__ scale, 
 }
 
 // ---------------------------------------------------------------- q = 4, M = 2 (one uint32 per block)
-template <int DT, int MODE>
+template <int DT, int MODE, bool LITERAL>
 __global__ void __launch_bounds__(kThreads)
 k_encode_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
               uint32_t* __restrict__ codes) {
@@ -197,7 +197,7 @@ k_encode_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::T
     float s = load_scale<MODE>(scale, td, b);
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = scale_in<MODE>(v[i], s);
-    codes[b] = e8::encode_q4m2(v);
+    codes[b] = e8::encode_q4m2<LITERAL>(v);
 }
 
 template <int DT, int MODE>
@@ -207,11 +207,10 @@ k_decode_q4m2(const uint32_t* __restrict__ codes, const float* __restrict__ scal
     int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (b >= n) return;
     uint32_t code = __ldg(codes + b);
-    float xh[8];
-    e8::decode_q4m2(code, table, xh);
     float s = load_scale<MODE>(scale, td, b);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) xh[i] = scale_out<MODE>(xh[i], s);
+    float v2[8], xh[8];
+    e8::decode_q4m2_twice(code, table, v2);
+    e8::scale_twice<MODE>(v2, s, xh);
     e8::Row8<DT>::store(out, b, xh);
 }
 
@@ -226,17 +225,18 @@ k_quantize_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8:
     float s = load_scale<MODE>(scale, td, b);
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = scale_in<MODE>(v[i], s);
-    uint32_t code = e8::encode_q4m2(v);
+    uint32_t code = e8::encode_q4m2<false>(v);
     if (codes) codes[b] = code;
-    float xh[8];
-    e8::decode_q4m2(code, table, xh);
+    float v2[8], xh[8];
+    e8::decode_q4m2_twice(code, table, v2);
+    e8::scale_twice<MODE>(v2, s, xh);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) xh[i] = clampf(scale_out<MODE>(xh[i], s), clip);
+    for (int i = 0; i < 8; ++i) xh[i] = clampf(xh[i], clip);
     e8::Row8<DTO>::store(out, b, xh);
 }
 
 // Residual table of the q=4 decoder, produced by the literal float32 decoder itself:
-// entry[w] = 2 * (G b - 4 Q(G b / 4)) for the 16-bit level word w, as 8 int8.
+// entry[w] = 2 * (G b - 4 Q(G b / 4)) + 7 for the 16-bit level word w, as 8 unsigned bytes.
 __global__ void k_build_table_q4(uint2* __restrict__ table) {
     int w = blockIdx.x * blockDim.x + threadIdx.x;
     if (w >= 65536) return;
@@ -247,8 +247,8 @@ __global__ void k_build_table_q4(uint2* __restrict__ table) {
     uint32_t lo = 0, hi = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        lo |= ((uint32_t)(__float2int_rn(__fmul_rn(r[i], 2.0f)) & 0xff)) << (8 * i);
-        hi |= ((uint32_t)(__float2int_rn(__fmul_rn(r[i + 4], 2.0f)) & 0xff)) << (8 * i);
+        lo |= ((uint32_t)((__float2int_rn(__fmul_rn(r[i], 2.0f)) + e8::kTableBias) & 0xff)) << (8 * i);
+        hi |= ((uint32_t)((__float2int_rn(__fmul_rn(r[i + 4], 2.0f)) + e8::kTableBias) & 0xff)) << (8 * i);
     }
     table[w] = make_uint2(lo, hi);
 }
@@ -358,14 +358,16 @@ int coset_e8_encode(const void* x, int x_dtype, const float* scale, int scale_mo
     if (int e = check_common(x, codes, n_blocks, q, M)) return e;
     if (int e = check_scale(scale, scale_mode, blocks_per_tile)) return e;
     if (x_dtype != COSET_DTYPE_F32 && x_dtype != COSET_DTYPE_BF16) return fail(COSET_E_BADARG, "unknown x_dtype %d", x_dtype);
-    if (sem != COSET_SEM_CORE) return fail(COSET_E_UNSUPPORTED, "semantics %d not available in this entry point", sem);
+    if (sem != COSET_SEM_CORE && sem != COSET_SEM_CORE_LITERAL) return fail(COSET_E_UNSUPPORTED, "semantics %d not available in this entry point", sem);
     if (n_blocks == 0) return 0;
     if (!aligned(x, 16) || !aligned(codes, 4)) return fail(COSET_E_ALIGN, "x must be 16-byte and codes 4-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
     e8::TileDiv td = e8::make_tile_div(scale_mode == COSET_SCALE_MUL_TILE ? blocks_per_tile : 1, n_blocks);
     unsigned grid = grid_for(n_blocks);
-    if (q == 4 && M == 2) {
-        DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2<DT, MODE><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes))))
+    if (q == 4 && M == 2 && sem == COSET_SEM_CORE) {
+        DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2<DT, MODE, false><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes))))
+    } else if (q == 4 && M == 2) {
+        DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2<DT, MODE, true><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes))))
     } else if (q <= 4) {
         DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_generic<DT, MODE, 2><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, q, M, codes))))
     } else {

@@ -26,11 +26,13 @@ template <int DTG, bool Q4>
 __device__ __forceinline__ float bwd_block(const void* __restrict__ g, const float* __restrict__ w,
                                            const void* __restrict__ codes, const uint2* __restrict__ table, float beta,
                                            float clip, int q, int64_t b, float* __restrict__ dw) {
-    float gv[8], wv[8], qv[8], out[8];
+    float gv[8], wv[8], qv[8], uv[8], out[8];
     e8::Row8<DTG>::load(g, b, gv);
     e8::Row8<0>::load(w, b, wv);
     if (Q4) {
-        e8::decode_q4m2(__ldg(reinterpret_cast<const uint32_t*>(codes) + b), table, qv);
+        float v2[8];
+        e8::decode_q4m2_twice(__ldg(reinterpret_cast<const uint32_t*>(codes) + b), table, v2);
+        e8::scale_twice<2>(v2, beta, uv);
     } else {
         uint32_t words[2];
         if (q <= 4) {
@@ -52,11 +54,13 @@ __device__ __forceinline__ float bwd_block(const void* __restrict__ g, const flo
             for (int i = 0; i < 8; ++i) qv[i] = __fadd_rn(qv[i], __fmul_rn(wgt, r[i]));
             wgt = __fmul_rn(wgt, qf);
         }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) uv[i] = __fdiv_rn(qv[i], beta);
     }
     float acc = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        float u = __fdiv_rn(qv[i], beta);
+        float u = uv[i];
         bool pass = (clip > 0.0f) ? (u >= -clip && u <= clip) : (u == u);
         float gc = pass ? gv[i] : 0.0f;
         float t = __fdiv_rn(gc, beta);

@@ -29,6 +29,9 @@
  * Semantics modes
  *   COSET_SEM_CORE  bit-exact with coset.core.e8 (float32; including its g_x flip rule and its
  *                   level recurrence without re-quantisation)
+ *   COSET_SEM_CORE_LITERAL  identical results to COSET_SEM_CORE by construction of the slow path:
+ *                   every block runs the op-by-op restatement, none the guarded fast path; the
+ *                   tests use it to cross-check the fast path on inputs too large for the CPU oracle
  *   COSET_SEM_REF   bit-exact with ref/hnlq.py (float64, tie dither, re-quantising recurrence,
  *                   overload loop); parity-only, not a timed path
  *
@@ -53,6 +56,7 @@ extern "C" {
 
 #define COSET_SEM_CORE 0
 #define COSET_SEM_REF 1
+#define COSET_SEM_CORE_LITERAL 2 /* same results as CORE, every block through the op-by-op search (validation) */
 
 #define COSET_E_BADARG (-1)   /* null pointer, negative size, unknown enum */
 #define COSET_E_UNSUPPORTED (-2) /* q / M / dtype combination not implemented */

@@ -228,3 +228,66 @@ def test_dither_path(e8, cfgcls):
     digits, _ = e8.e8_encode(x.cuda(), c, dither=d.cuda())
     xs = (x.numpy() / np.float32(0.3) + d.numpy()[None]).astype(np.float32)
     assert np.array_equal(digits.cpu().numpy().astype(np.int64), O.codes_to_int(O.encode(xs)))
+
+
+# ---------------------------------------------------------------------------------------------
+# Full-size properties: inputs far too large for the CPU oracle are cross-checked between the
+# guarded fast path and the op-by-op search (two independent evaluations inside the library;
+# the op-by-op one is what the golden / oracle tests above pin).
+@pytest.mark.parametrize("scale", [0.02, 0.125, 0.5, 1.0, 3.0, 20.0, 200.0])
+def test_fast_path_equals_literal_at_full_size(e8, scale):
+    g = torch.Generator(device="cuda").manual_seed(int(scale * 1000))
+    n = 1 << 24
+    x = torch.randn(n, 8, device="cuda", generator=g) * scale
+    fast = e8.e8_encode_packed(x).view(torch.int32)
+    lit = e8.e8_encode_packed(x, literal=True).view(torch.int32)
+    assert torch.equal(fast, lit), int((fast != lit).sum())
+    if 0.1 < scale < 5:
+        assert (fast != 0).float().mean() > 0.5  # not the degenerate all-zero regime
+
+
+def test_fast_path_equals_literal_on_structured_inputs(e8):
+    g = torch.Generator(device="cuda").manual_seed(77)
+    n = 1 << 22
+    cases = []
+    cases.append(torch.randint(-16, 17, (n, 8), device="cuda", generator=g).float() / 8)        # decoder-like ties
+    cases.append(torch.randint(-6, 7, (n, 8), device="cuda", generator=g).float() / 2)          # lattice points
+    x = torch.randn(n, 8, device="cuda", generator=g)
+    x[torch.rand(n, 8, device="cuda", generator=g) < 0.3] = 0.0                                  # sparse
+    cases.append(x)
+    x = torch.randn(n, 8, device="cuda", generator=g) * 2
+    k = torch.randint(0, 8, (n,), device="cuda", generator=g)
+    near = torch.randint(-4, 5, (n,), device="cuda", generator=g).float() + 0.5
+    near = near + torch.randint(-3, 4, (n,), device="cuda", generator=g).float() * 2.0 ** -23    # a few ulps around a tie
+    x[torch.arange(n, device="cuda"), k] = near
+    cases.append(x)
+    cases.append(torch.zeros(n, 8, device="cuda"))
+    for x in cases:
+        fast = e8.e8_encode_packed(x).view(torch.int32)
+        lit = e8.e8_encode_packed(x, literal=True).view(torch.int32)
+        assert torch.equal(fast, lit), int((fast != lit).sum())
+
+
+def test_bulk_config_properties(e8):
+    """BASELINE bulk config at full size (2^25 blocks): fused round trip == decode(encode), the
+    reconstruction error is bounded by the covering radius wherever the quantiser is not
+    overloaded, and re-quantising a reconstruction is idempotent for the inner level."""
+    from coset_b200 import _lib
+    g = torch.Generator(device="cuda").manual_seed(0)
+    n = 1 << 25
+    x = torch.randn(n, 8, device="cuda", generator=g) * 0.02
+    beta = torch.full((n,), 25.0, device="cuda")
+    MT = _lib.SCALE_MUL_TILE
+    codes = e8.e8_encode_packed(x, scale=beta, scale_mode=MT)
+    xh = e8.e8_decode_packed(codes, scale=beta, scale_mode=MT)
+    fused = torch.empty_like(x)
+    rc = _lib.lib().coset_e8_quantize(_lib.ptr(x), 0, _lib.ptr(beta), MT, n, 1, 4, 2, 0.0, _lib.ptr(fused), 0, None,
+                                      _lib.stream())
+    assert rc == 0
+    assert torch.equal(fused, xh)
+    err = ((xh - x) * 25.0).norm(dim=1)
+    inside = (x * 25.0).abs().amax(dim=1) < 3.0
+    assert float(err[inside].max()) < 1.0  # E8 covering radius sqrt(2)/2 plus the coarse-level slack
+    codes2 = e8.e8_encode_packed(xh, scale=beta, scale_mode=MT)
+    same = (codes2.view(torch.int32) == codes.view(torch.int32)).float().mean()
+    assert same > 0.75  # core semantics: decode(encode(x)) is a fixed point for most blocks (reference: ~79 %)

@@ -71,9 +71,13 @@ def test_layer_forward_backward_row_tiling(golden_layer, tag):
     y = layer(x)
     ((y - dev(g[f"{tag}_t"])) ** 2).mean().backward()
     wq = layer._quantize_weights().detach().cpu().numpy()
-    mism = (bits(wq) != bits(g[f"{tag}_Wq"])).mean()
-    assert mism < 2e-3, mism  # only rows whose beta differs in the last bit can differ
-    if mism == 0:
+    # A row whose beta differs from the CPU value in the last bit rescales by that bit; a changed
+    # code would show as an O(1) jump, which must stay a rare boundary event.
+    want_wq = g[f"{tag}_Wq"]
+    jumps = (np.abs(wq - want_wq) > 1e-4 * np.maximum(np.abs(want_wq), 1e-3)).mean()
+    assert jumps < 2e-3, jumps
+    if jumps == 0:
+        assert rel(wq, want_wq) < 1e-6
         assert rel(y.detach().cpu().numpy(), g[f"{tag}_y"]) < 1e-5
         assert rel(layer.weight.grad.cpu().numpy(), g[f"{tag}_dW"]) < 1e-5
         assert rel(x.grad.cpu().numpy(), g[f"{tag}_dx"]) < 1e-5
