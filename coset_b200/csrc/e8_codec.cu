@@ -66,7 +66,10 @@ __device__ __forceinline__ float scale_out(float v, float s) {
 template <int MODE>
 __device__ __forceinline__ float load_scale(const float* scale, const e8::TileDiv& td, int64_t block) {
     if (MODE == COSET_SCALE_DIV_SCALAR) return __ldg(scale);
-    if (MODE == COSET_SCALE_MUL_TILE) return __ldg(scale + e8::tile_of(td, block));
+    if (MODE == COSET_SCALE_MUL_TILE) {
+        // per-block scales are streamed once; per-row scales are reused by the whole row
+        return td.divisor == 1 ? __ldcs(scale + block) : __ldg(scale + e8::tile_of(td, block));
+    }
     return 1.0f;
 }
 
@@ -187,7 +190,7 @@ k_quantize_generic(const void* __restrict__ x, const float* __restrict__ scale, 
 
 // ---------------------------------------------------------------- q = 4, M = 2 (one uint32 per block)
 template <int DT, int MODE, bool LITERAL>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 6)
 k_encode_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
               uint32_t* __restrict__ codes) {
     int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
@@ -197,21 +200,35 @@ k_encode_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::T
     float s = load_scale<MODE>(scale, td, b);
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = scale_in<MODE>(v[i], s);
-    codes[b] = e8::encode_q4m2<LITERAL>(v);
+    __stcs(codes + b, e8::encode_q4m2<LITERAL>(v));
 }
 
+// Two blocks per thread (kThreads apart, so every access stays coalesced): both codes are
+// loaded before the first table lookup, which doubles the gathers in flight per thread.
+constexpr int kDecPerThread = 2;
 template <int DT, int MODE>
 __global__ void __launch_bounds__(kThreads)
 k_decode_q4m2(const uint32_t* __restrict__ codes, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
               const uint2* __restrict__ table, void* __restrict__ out) {
-    int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    if (b >= n) return;
-    uint32_t code = __ldg(codes + b);
-    float s = load_scale<MODE>(scale, td, b);
-    float v2[8], xh[8];
-    e8::decode_q4m2_twice(code, table, v2);
-    e8::scale_twice<MODE>(v2, s, xh);
-    e8::Row8<DT>::store(out, b, xh);
+    int64_t base = (int64_t)blockIdx.x * (kThreads * kDecPerThread) + threadIdx.x;
+    uint32_t code[kDecPerThread];
+    float s[kDecPerThread];
+#pragma unroll
+    for (int j = 0; j < kDecPerThread; ++j) {
+        int64_t b = base + j * kThreads;
+        code[j] = b < n ? __ldcs(codes + b) : 0u;
+        s[j] = b < n ? load_scale<MODE>(scale, td, b) : 1.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < kDecPerThread; ++j) {
+        int64_t b = base + j * kThreads;
+        if (b < n) {
+            float v2[8], xh[8];
+            e8::decode_q4m2_twice(code[j], table, v2);
+            e8::scale_twice<MODE>(v2, s[j], xh);
+            e8::Row8<DT>::store(out, b, xh);
+        }
+    }
 }
 
 template <int DTI, int DTO, int MODE>
@@ -390,7 +407,8 @@ int coset_e8_decode(const void* codes, const float* scale, int scale_mode, int64
     if (q == 4 && M == 2) {
         const uint2* table = residual_table_q4(st);
         if (!table) return COSET_E_STATE;
-        DISPATCH_DT(out_dtype, DT, DISPATCH_MODE(scale_mode, (k_decode_q4m2<DT, MODE><<<grid, kThreads, 0, st>>>((const uint32_t*)codes, scale, td, n_blocks, table, out))))
+        unsigned grid2 = (unsigned)((n_blocks + kThreads * kDecPerThread - 1) / (kThreads * kDecPerThread));
+        DISPATCH_DT(out_dtype, DT, DISPATCH_MODE(scale_mode, (k_decode_q4m2<DT, MODE><<<grid2, kThreads, 0, st>>>((const uint32_t*)codes, scale, td, n_blocks, table, out))))
     } else if (q <= 4) {
         DISPATCH_DT(out_dtype, DT, DISPATCH_MODE(scale_mode, (k_decode_generic<DT, MODE, 2><<<grid, kThreads, 0, st>>>(codes, scale, td, n_blocks, q, M, out))))
     } else {

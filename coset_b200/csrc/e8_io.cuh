@@ -45,21 +45,21 @@ template <>
 struct Row8<0> {  // float32
     static __device__ __forceinline__ void load(const void* base, int64_t block, float (&v)[8]) {
         const float4* p = reinterpret_cast<const float4*>(base) + block * 2;
-        float4 a = __ldg(p), b = __ldg(p + 1);
+        float4 a = __ldcs(p), b = __ldcs(p + 1);  // streamed once: do not displace the residual table in L1
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
         v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
     }
     static __device__ __forceinline__ void store(void* base, int64_t block, const float (&v)[8]) {
         float4* p = reinterpret_cast<float4*>(base) + block * 2;
-        p[0] = make_float4(v[0], v[1], v[2], v[3]);
-        p[1] = make_float4(v[4], v[5], v[6], v[7]);
+        __stcs(p, make_float4(v[0], v[1], v[2], v[3]));
+        __stcs(p + 1, make_float4(v[4], v[5], v[6], v[7]));
     }
 };
 
 template <>
 struct Row8<1> {  // bf16: widened exactly on load, rounded to nearest-even on store
     static __device__ __forceinline__ void load(const void* base, int64_t block, float (&v)[8]) {
-        uint4 a = __ldg(reinterpret_cast<const uint4*>(base) + block);
+        uint4 a = __ldcs(reinterpret_cast<const uint4*>(base) + block);
         uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -74,7 +74,7 @@ struct Row8<1> {  // bf16: widened exactly on load, rounded to nearest-even on s
             __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
             w[i] = *reinterpret_cast<uint32_t*>(&h);
         }
-        reinterpret_cast<uint4*>(base)[block] = make_uint4(w[0], w[1], w[2], w[3]);
+        __stcs(reinterpret_cast<uint4*>(base) + block, make_uint4(w[0], w[1], w[2], w[3]));
     }
 };
 

@@ -242,7 +242,7 @@ def test_fast_path_equals_literal_at_full_size(e8, scale):
     fast = e8.e8_encode_packed(x).view(torch.int32)
     lit = e8.e8_encode_packed(x, literal=True).view(torch.int32)
     assert torch.equal(fast, lit), int((fast != lit).sum())
-    if 0.1 < scale < 5:
+    if 0.4 < scale < 5:
         assert (fast != 0).float().mean() > 0.5  # not the degenerate all-zero regime
 
 
