@@ -20,6 +20,7 @@ SOURCES = [
     "e8_codec.cu",
     "e8_layer.cu",
     "e8_host.cu",
+    "e8_gradcomm.cu",
 ]
 
 NVCC_FLAGS = [

@@ -1,0 +1,76 @@
+// Decode-and-average for the E8-quantised gradient exchange.
+//
+// Every rank encodes its gradient with one shared scalar scale s (x * s, then q=4, M=2 codes),
+// the packed codes are all-gathered into a [W, n_blocks] array in LOCAL memory, and this kernel
+// reads the W code streams once and writes
+//     out = ( sum_r x_hat_r ) / (s * W)
+// The sum of reconstructions is exact (half-integers, accumulated as integers), the divisor
+// d = RN(s * W) is formed once in float32 and the quotient is one IEEE division, so a CPU run of
+// the same recipe is bit-identical.  No pointer to another GPU's memory is ever dereferenced.
+//
+// Bytes per block: W * 4 read + 32 written (float32 output).
+#include "common.cuh"
+#include "e8_fast.cuh"
+#include "e8_io.cuh"
+
+using namespace coset;
+
+namespace {
+
+constexpr int kThreads = 256;
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads)
+k_decode_mean(const uint32_t* __restrict__ codes, int world, int64_t n, int64_t stride, float divisor,
+              const uint2* __restrict__ table, void* __restrict__ out) {
+    int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (b >= n) return;
+    // 16-bit lanes: acc[0] = coordinates (0,2), acc[1] = (1,3), acc[2] = (4,6), acc[3] = (5,7)
+    uint32_t acc[4] = {0u, 0u, 0u, 0u};
+    for (int r = 0; r < world; ++r) {
+        uint32_t code = __ldcs(codes + (int64_t)r * stride + b);
+        uint2 t0 = __ldg(table + (code & 0xffffu));
+        uint2 t1 = __ldg(table + (code >> 16));
+        uint32_t lo = t0.x + 4u * t1.x, hi = t0.y + 4u * t1.y;  // biased bytes, each <= 90
+        acc[0] += lo & 0x00ff00ffu;
+        acc[1] += (lo >> 8) & 0x00ff00ffu;
+        acc[2] += hi & 0x00ff00ffu;
+        acc[3] += (hi >> 8) & 0x00ff00ffu;
+    }
+    const int bias = 5 * e8::kTableBias * world;  // every rank contributes 7 + 4*7 to each lane
+    int v[8];
+    v[0] = (int)(acc[0] & 0xffffu) - bias; v[2] = (int)(acc[0] >> 16) - bias;
+    v[1] = (int)(acc[1] & 0xffffu) - bias; v[3] = (int)(acc[1] >> 16) - bias;
+    v[4] = (int)(acc[2] & 0xffffu) - bias; v[6] = (int)(acc[2] >> 16) - bias;
+    v[5] = (int)(acc[3] & 0xffffu) - bias; v[7] = (int)(acc[3] >> 16) - bias;
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float sum = __fmul_rn((float)v[i], 0.5f);  // exact: |v| < 2^16
+        o[i] = __fdiv_rn(sum, divisor);
+    }
+    e8::Row8<DT>::store(out, b, o);
+}
+
+}  // namespace
+
+extern "C" int coset_e8_decode_mean(const void* codes, int world, int64_t n_blocks, int64_t rank_stride_blocks,
+                                    float scale, void* out, int out_dtype, void* stream) {
+    if (world < 1 || world > 512) return fail(COSET_E_BADARG, "world must be in 1..512");
+    if (n_blocks < 0 || rank_stride_blocks < n_blocks) return fail(COSET_E_BADARG, "bad n_blocks / rank stride");
+    if (n_blocks == 0) return 0;
+    if (!codes || !out) return fail(COSET_E_BADARG, "null pointer");
+    if (out_dtype != COSET_DTYPE_F32 && out_dtype != COSET_DTYPE_BF16) return fail(COSET_E_BADARG, "unknown out_dtype");
+    if (!aligned(codes, 4) || !aligned(out, 16)) return fail(COSET_E_ALIGN, "codes must be 4-byte and out 16-byte aligned");
+    if (!(scale == scale) || scale == 0.0f) return fail(COSET_E_BADARG, "scale must be a non-zero number");
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint2* table = residual_table_q4(st);
+    if (!table) return COSET_E_STATE;
+    float divisor = scale * (float)world;  // one float32 rounding, reproduced by the CPU recipe
+    unsigned grid = (unsigned)((n_blocks + kThreads - 1) / kThreads);
+    if (out_dtype == COSET_DTYPE_F32)
+        k_decode_mean<0><<<grid, kThreads, 0, st>>>((const uint32_t*)codes, world, n_blocks, rank_stride_blocks, divisor, table, out);
+    else
+        k_decode_mean<1><<<grid, kThreads, 0, st>>>((const uint32_t*)codes, world, n_blocks, rank_stride_blocks, divisor, table, out);
+    return check_launch("e8_decode_mean");
+}

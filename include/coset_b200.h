@@ -148,6 +148,17 @@ int coset_e8_decode_host(coset_host_ctx* ctx, const void* codes_host, const floa
                          int scale_mode, int64_t n_blocks, int64_t blocks_per_tile, int q, int M,
                          void* out_host, int out_dtype);
 
+/*
+ * E8-quantised gradient exchange, receive side.  The reference only plans this path
+ * ("quantize gradient buckets ... decode", prompts/design_instructions.md:104-110); the recipe is:
+ * every rank encodes x * scale with coset_e8_encode (q=4, M=2, COSET_SCALE_MUL_TILE with a single
+ * tile), the packed codes are all-gathered into codes[world][rank_stride_blocks] in local memory,
+ * and this call writes  out = (sum_r x_hat_r) / RN(scale * world)  as [n_blocks, 8].
+ * The sum is exact, the division is one IEEE float32 division.
+ */
+int coset_e8_decode_mean(const void* codes, int world, int64_t n_blocks, int64_t rank_stride_blocks,
+                         float scale, void* out, int out_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

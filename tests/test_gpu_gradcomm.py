@@ -1,0 +1,83 @@
+"""E8 gradient exchange on the GPU: the decode-and-average kernel against the CPU recipe, and
+the NCCL exchange on 2 GPUs (skipped when only one is visible)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bits
+from gradcomm_util import cpu_decode_mean
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+def test_decode_mean_matches_cpu_recipe(world):
+    from coset_b200.gradcomm import CudaCodec
+    n, scale = 5000, 500.0
+    codec = CudaCodec()
+    gathered = torch.empty((world, n), dtype=torch.int32, device="cuda")
+    digits = []
+    for r in range(world):
+        g = torch.Generator().manual_seed(1000 + r)
+        grad = (torch.randn(n, 8, generator=g) * 1e-3)
+        codec.encode(grad.cuda(), scale, gathered[r])
+        d = O.encode(grad.numpy(), beta=np.array([scale], np.float32), scale_mode=2, blocks_per_tile=n)
+        assert np.array_equal(gathered[r].cpu().numpy().view(np.uint32), O.pack_q4(d))
+        digits.append(d)
+    out = torch.empty((n, 8), device="cuda")
+    codec.decode_mean(gathered, world, n, scale, out)
+    assert np.array_equal(bits(out.cpu().numpy()), bits(cpu_decode_mean(digits, scale)))
+
+
+def test_single_gpu_exchange_roundtrip():
+    from coset_b200.gradcomm import E8GradientExchange
+    g = torch.randn(8 * 4096 + 3, device="cuda") * 1e-3
+    avg = E8GradientExchange(scale=500.0).all_reduce_mean(g)
+    assert avg.shape == g.shape
+    assert float((avg - g).abs().max()) < 1.6 / 500.0
+
+
+WORKER = r'''
+import os, sys, numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+from coset_b200.gradcomm import E8GradientExchange
+from gradcomm_util import cpu_decode_mean
+from oracle import oracle as O
+n_values = 8 * 20000 + 6
+g = torch.Generator().manual_seed(1000 + rank)
+grad = torch.randn(n_values, generator=g) * 1e-3
+avg = E8GradientExchange(scale=500.0).all_reduce_mean(grad.cuda())
+torch.cuda.synchronize()
+if rank == 0:
+    digits = []
+    for r in range(world):
+        gg = torch.Generator().manual_seed(1000 + r)
+        x = torch.randn(n_values, generator=gg) * 1e-3
+        p = np.zeros(((n_values + 7) // 8) * 8, np.float32); p[:n_values] = x.numpy()
+        digits.append(O.encode(p.reshape(-1, 8), beta=np.array([500.0], np.float32), scale_mode=2, blocks_per_tile=p.size // 8))
+    want = cpu_decode_mean(digits, 500.0).reshape(-1)[:n_values]
+    assert np.array_equal(avg.cpu().numpy(), want), "exchange differs from the CPU recipe"
+    print("EXCHANGE_OK")
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_nccl_exchange(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29617", str(script), ROOT]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert "EXCHANGE_OK" in res.stdout

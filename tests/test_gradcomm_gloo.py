@@ -1,0 +1,66 @@
+"""Host logic of the E8 gradient exchange on CPU ranks (gloo, world size 2): padding, gather
+layout, averaging recipe.  The device codec is replaced by the oracle-backed stand-in; the CUDA
+kernels themselves are covered by the gpu tests."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _worker(rank, world, port, n_values, out_dir):
+    sys.path.insert(0, os.path.dirname(HERE))
+    sys.path.insert(0, HERE)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from coset_b200.gradcomm import E8GradientExchange
+    from gradcomm_util import OracleCodec
+    g = torch.Generator().manual_seed(1000 + rank)
+    grad = torch.randn(n_values, generator=g) * 1e-3
+    ex = E8GradientExchange(scale=500.0, codec=OracleCodec())
+    avg = ex.all_reduce_mean(grad)
+    np.save(os.path.join(out_dir, f"avg{rank}.npy"), avg.numpy())
+    dist.destroy_process_group()
+
+
+def test_two_rank_exchange_matches_single_process_recipe(tmp_path):
+    from oracle import oracle as O
+    from gradcomm_util import cpu_decode_mean
+    world, n_values = 2, 8 * 1000 + 5  # ragged tail: padded with zeros and stripped
+    port = 29500 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(world, port, n_values, str(tmp_path)), nprocs=world, join=True)
+    got = [np.load(tmp_path / f"avg{r}.npy") for r in range(world)]
+    assert np.array_equal(got[0], got[1])  # every rank holds the same bits
+    codes = []
+    grads = []
+    for r in range(world):
+        g = torch.Generator().manual_seed(1000 + r)
+        grad = torch.randn(n_values, generator=g) * 1e-3
+        grads.append(grad.numpy())
+        padded = np.zeros(((n_values + 7) // 8) * 8, np.float32)
+        padded[:n_values] = grad.numpy()
+        codes.append(O.encode(padded.reshape(-1, 8), beta=np.array([500.0], np.float32), scale_mode=2,
+                              blocks_per_tile=padded.size // 8))
+    want = cpu_decode_mean(codes, 500.0).reshape(-1)[:n_values]
+    assert np.array_equal(got[0], want)
+    true_mean = (grads[0] + grads[1]) / 2
+    # per-value error: at most 1.5 lattice units (the reference flip rule can move a coordinate
+    # away from the input), i.e. 1.5 / scale, averaged over the ranks
+    assert np.abs(got[0] - true_mean).max() < 1.6 / 500.0
+    rel = np.linalg.norm(got[0] - true_mean) / np.linalg.norm(true_mean)
+    assert rel < 1.0, rel
+
+
+def test_single_process_without_process_group():
+    sys.path.insert(0, HERE)
+    from coset_b200.gradcomm import E8GradientExchange
+    from gradcomm_util import OracleCodec
+    grad = torch.randn(64) * 1e-3
+    avg = E8GradientExchange(scale=500.0, codec=OracleCodec()).all_reduce_mean(grad)
+    assert avg.shape == grad.shape
+    assert (avg - grad).abs().max() < 1.6 / 500.0
