@@ -21,6 +21,7 @@ SOURCES = [
     "e8_layer.cu",
     "e8_host.cu",
     "e8_gradcomm.cu",
+    "e8_vlut.cu",
 ]
 
 NVCC_FLAGS = [

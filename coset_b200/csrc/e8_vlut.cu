@@ -1,0 +1,131 @@
+// Code-domain matrix product for inference: y[T, N] = x[T, K] * Wq^T (+ bias), with the weight
+// held only as packed E8 codes (q=4, M=2: 4 B per 8 weights) plus its scales.
+//
+// The reference defines the math through per-query lookup tables of inner products with every
+// codeword residual, <y, x_hat> = sum_m q^m <y, r(b_m)> (coset/legacy/quant/vlut.py:72-117,
+// driver tests/legacy/test_one_sided_vlut_pytest.py:22-43); a table of 4^8 inner products per
+// 8 activations is 128 MB per token at K = 4096, so the GPU form keeps ONE table (the 65536
+// residuals r(b), 512 KB, L2/L1 resident), rebuilds the weight block in registers and multiplies:
+//     w = (r(b_0) + 4 r(b_1)) / beta        (same IEEE division as the training layer)
+//     y += <w, x_block>
+// Small T ("GEMV" regime): memory-bound on the code stream, 4 B (+ scale) per 8 weights.
+// One warp owns one output row; lanes stride over the row's blocks (coalesced 128 B of codes per
+// step), keep TT token accumulators in registers and reduce with shuffles at the end.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "e8_fast.cuh"
+#include "e8_io.cuh"
+
+using namespace coset;
+
+namespace {
+
+constexpr int kWarps = 8;
+
+template <int XDT>
+__device__ __forceinline__ void load_x8(const void* x, int64_t elem_offset, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load_x8<0>(const void* x, int64_t off, float (&v)[8]) {
+    const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + off);
+    float4 a = __ldg(p), b = __ldg(p + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load_x8<1>(const void* x, int64_t off, float (&v)[8]) {
+    uint4 a = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + off));
+    uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+template <int TT, int XDT, int MODE>
+__global__ void __launch_bounds__(kWarps * 32)
+k_vlut_gemv(const uint32_t* __restrict__ codes, const float* __restrict__ beta, e8::TileDiv td, int n_out, int kb,
+            const void* __restrict__ x, int64_t ldx, int T, const float* __restrict__ bias,
+            const uint2* __restrict__ table, float* __restrict__ y, int64_t ldy) {
+    int row = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    int lane = threadIdx.x & 31;
+    int t0 = blockIdx.y * TT;
+    if (row >= n_out) return;
+    float acc[TT];
+#pragma unroll
+    for (int t = 0; t < TT; ++t) acc[t] = 0.0f;
+    const int64_t row_base = (int64_t)row * kb;
+    for (int blk = lane; blk < kb; blk += 32) {
+        uint32_t code = __ldcs(codes + row_base + blk);
+        float s = 1.0f;
+        if (MODE == COSET_SCALE_MUL_TILE) s = __ldg(beta + e8::tile_of(td, row_base + blk));
+        float v2[8], w[8];
+        e8::decode_q4m2_twice(code, table, v2);
+        e8::scale_twice<MODE == COSET_SCALE_MUL_TILE ? 2 : 0>(v2, s, w);
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+            if (t0 + t < T) {
+                float xv[8];
+                load_x8<XDT>(x, (int64_t)(t0 + t) * ldx + (int64_t)blk * 8, xv);
+                float a = acc[t];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) a = __fmaf_rn(w[i], xv[i], a);
+                acc[t] = a;
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < TT; ++t) {
+        float a = acc[t];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane == 0 && t0 + t < T) y[(int64_t)(t0 + t) * ldy + row] = a + (bias ? __ldg(bias + row) : 0.0f);
+    }
+}
+
+template <int XDT, int MODE>
+void launch_gemv(int tt, dim3 grid, cudaStream_t st, const uint32_t* codes, const float* beta, e8::TileDiv td, int n_out,
+                 int kb, const void* x, int64_t ldx, int T, const float* bias, const uint2* table, float* y, int64_t ldy) {
+#define GEMV_CASE(TT) k_vlut_gemv<TT, XDT, MODE><<<grid, kWarps * 32, 0, st>>>(codes, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy)
+    switch (tt) {
+        case 1: GEMV_CASE(1); break;
+        case 2: GEMV_CASE(2); break;
+        case 4: GEMV_CASE(4); break;
+        case 8: GEMV_CASE(8); break;
+        default: GEMV_CASE(16); break;
+    }
+#undef GEMV_CASE
+}
+
+}  // namespace
+
+extern "C" int coset_e8_vlut_gemv(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
+                                  const void* x, int x_dtype, int64_t ldx, int T, const float* bias, float* y,
+                                  int64_t ldy, void* stream) {
+    if (n_out < 0 || n_in < 0 || T < 0 || (n_in % 8) != 0) return fail(COSET_E_BADARG, "bad shape (n_in must be a multiple of 8)");
+    if (n_out == 0 || T == 0) return 0;
+    if (!codes || !x || !y) return fail(COSET_E_BADARG, "null pointer");
+    if (x_dtype != COSET_DTYPE_F32 && x_dtype != COSET_DTYPE_BF16) return fail(COSET_E_BADARG, "unknown x_dtype");
+    if (ldx < n_in || ldy < n_out) return fail(COSET_E_BADARG, "leading dimension too small");
+    const int elem = x_dtype == COSET_DTYPE_F32 ? 4 : 2;
+    if (!aligned(x, 16) || ((ldx * elem) % 16) != 0 || !aligned(codes, 4))
+        return fail(COSET_E_ALIGN, "x rows must be 16-byte aligned and codes 4-byte aligned");
+    if (beta && blocks_per_tile < 1) return fail(COSET_E_BADARG, "blocks_per_tile must be >= 1");
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint2* table = residual_table_q4(st);
+    if (!table) return COSET_E_STATE;
+    int kb = n_in / 8;
+    e8::TileDiv td = e8::make_tile_div(beta ? blocks_per_tile : 1, (int64_t)n_out * kb);
+    int tt = T >= 16 ? 16 : (T >= 8 ? 8 : (T >= 4 ? 4 : (T >= 2 ? 2 : 1)));
+    dim3 grid((n_out + kWarps - 1) / kWarps, (T + tt - 1) / tt);
+    if (grid.y > 65535) return fail(COSET_E_UNSUPPORTED, "T too large for the small-T kernel");
+    const uint32_t* c = (const uint32_t*)codes;
+    if (x_dtype == COSET_DTYPE_F32) {
+        if (beta) launch_gemv<0, 2>(tt, grid, st, c, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy);
+        else launch_gemv<0, 0>(tt, grid, st, c, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy);
+    } else {
+        if (beta) launch_gemv<1, 2>(tt, grid, st, c, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy);
+        else launch_gemv<1, 0>(tt, grid, st, c, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy);
+    }
+    return check_launch("e8_vlut_gemv");
+}

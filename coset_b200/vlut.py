@@ -1,0 +1,106 @@
+"""Inference with weights kept as E8 codes: E8CodeLinear.
+
+The weight of a trained HNLQLinearQAT layer is exported as packed q=4, M=2 codes (4 bytes per 8
+weights) plus the scales beta, and applied without ever storing a dense copy:
+
+  * few tokens  (T <= small_t_max): the code-domain kernel coset_e8_vlut_gemv, bound by the code
+    stream (8.4 - 16.8 MB for a 4096 x 4096 weight instead of 64 MB of float32);
+  * many tokens: the weight is dequantised once into bf16 by the decode kernel and multiplied on
+    the tensor cores.
+
+The math is the reference's one-sided vLUT inner product (coset/legacy/quant/vlut.py:72-117) in
+the layer's scale convention W_q = decode(codes) / beta (coset/core/layers.py:453-460).
+"""
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from .core.e8.codecs import e8_decode_packed, e8_encode_packed
+
+
+def e8_vlut_matmul(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_per_tile: int, x: torch.Tensor,
+                   bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ Wq.T + bias with Wq = decode(codes) / beta; codes int32 [n_out, n_in / 8]; x [T, n_in]."""
+    _lib.require_cuda(codes, "codes")
+    _lib.require_cuda(x, "x")
+    if codes.dtype != torch.int32 or codes.dim() != 2 or not codes.is_contiguous():
+        raise ValueError("codes must be a contiguous int32 tensor [n_out, n_in / 8]")
+    n_out, kb = codes.shape
+    if x.dim() != 2 or x.shape[1] != kb * 8:
+        raise ValueError(f"x must be [T, {kb * 8}], got {tuple(x.shape)}")
+    x = x.contiguous()
+    T = x.shape[0]
+    y = torch.empty((T, n_out), dtype=torch.float32, device=x.device)
+    b = beta.to(torch.float32).contiguous().view(-1) if beta is not None else None
+    bias32 = bias.to(torch.float32).contiguous() if bias is not None else None
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().coset_e8_vlut_gemv(_lib.ptr(codes), _lib.ptr(b) if b is not None else None, int(blocks_per_tile),
+                                           n_out, kb * 8, _lib.ptr(x), _lib.dtype_code(x, "x"), x.stride(0), T,
+                                           _lib.ptr(bias32) if bias32 is not None else None, _lib.ptr(y), y.stride(0),
+                                           _lib.stream())
+    _lib.check(rc, "coset_e8_vlut_gemv")
+    return y
+
+
+class E8CodeLinear(nn.Module):
+    """Linear layer that owns E8 codes + scales instead of a dense weight (inference only)."""
+
+    def __init__(self, codes: torch.Tensor, beta: torch.Tensor, blocks_per_tile: int,
+                 bias: Optional[torch.Tensor] = None, small_t_max: int = 64):
+        super().__init__()
+        self.out_features, kb = codes.shape
+        self.in_features = kb * 8
+        self.blocks_per_tile = int(blocks_per_tile)
+        self.small_t_max = small_t_max
+        self.register_buffer("codes", codes.contiguous())
+        self.register_buffer("beta", beta.to(torch.float32).contiguous().view(-1))
+        self.register_buffer("bias", bias.detach().clone() if bias is not None else None)
+        self._dense = None  # bf16 copy, built on first large-T call
+
+    @classmethod
+    def from_weight(cls, weight: torch.Tensor, beta: torch.Tensor, blocks_per_tile: int, bias=None, **kw):
+        """Quantise a dense float32 weight [n_out, n_in] with scales beta (layer convention)."""
+        _lib.require_cuda(weight, "weight")
+        n_out, n_in = weight.shape
+        if n_in % 8:
+            raise ValueError(f"Input dimension {n_in} must be divisible by 8 for E8 lattice")
+        packed = e8_encode_packed(weight.contiguous().view(-1, 8), 4, 2, scale=beta.contiguous().view(-1),
+                                  scale_mode=_lib.SCALE_MUL_TILE, blocks_per_tile=blocks_per_tile)
+        codes = packed.view(torch.int32).view(n_out, n_in // 8)
+        return cls(codes, beta, blocks_per_tile, bias, **kw)
+
+    @classmethod
+    def from_qat_layer(cls, layer, **kw):
+        """Export of a trained HNLQLinearQAT (q must be 4): codes, scales and bias.
+
+        Note: the exported layer omits the training-time clamp to +-weight_clip_value."""
+        if layer.q != 4:
+            raise ValueError("E8CodeLinear stores q=4, M=2 codes")
+        with torch.no_grad():
+            beta = layer._beta().detach()
+            bpt = layer.blocks_per_row if layer.tiling == "row" else 1
+            return cls.from_weight(layer.weight.detach(), beta, bpt, layer.bias, **kw)
+
+    def dense_weight(self, dtype=torch.float32) -> torch.Tensor:
+        """Wq = decode(codes) / beta as a dense [n_out, n_in] tensor."""
+        w = e8_decode_packed(self.codes.view(-1), 4, 2, scale=self.beta, scale_mode=_lib.SCALE_MUL_TILE,
+                             blocks_per_tile=self.blocks_per_tile, dtype=dtype)
+        return w.view(self.out_features, self.in_features)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.in_features)
+        if x2.shape[0] <= self.small_t_max:
+            y = e8_vlut_matmul(self.codes, self.beta, self.blocks_per_tile, x2, self.bias)
+            y = y.to(x.dtype) if x.dtype != torch.float32 else y
+        else:
+            if x2.dtype == torch.float32:
+                y = torch.nn.functional.linear(x2, self.dense_weight(torch.float32), self.bias)
+            else:
+                if self._dense is None:
+                    self._dense = self.dense_weight(torch.bfloat16)
+                b = self.bias.to(x2.dtype) if self.bias is not None else None
+                y = torch.nn.functional.linear(x2, self._dense.to(x2.dtype), b)
+        return y.reshape(*lead, self.out_features)

@@ -159,6 +159,21 @@ int coset_e8_decode_host(coset_host_ctx* ctx, const void* codes_host, const floa
 int coset_e8_decode_mean(const void* codes, int world, int64_t n_blocks, int64_t rank_stride_blocks,
                          float scale, void* out, int out_dtype, void* stream);
 
+/*
+ * Code-domain ("vLUT") product for inference, small token counts:
+ *   y[T, n_out] = x[T, n_in] * Wq^T + bias,   Wq = decode(codes) / beta   (never materialised)
+ * Math of the reference's one-sided vLUT inner product (coset/legacy/quant/vlut.py:72-117):
+ * <x, w_hat> = sum_m 4^m <x, r(b_m)>, r(b) = G b - 4 Q(G b / 4).
+ *   codes : [n_out, n_in/8] packed q=4, M=2 codes (row-major, as coset_e8_quantize emits them)
+ *   beta  : per-tile scale in the layer convention (may be NULL = no scale);
+ *           blocks_per_tile = n_in/8 for one scale per row, 1 for one per block
+ *   x     : [T, ldx] float32 or bf16 (rows 16-byte aligned);  y: [T, ldy] float32
+ * Memory-bound on the code stream; meant for T <= ~64 (larger T: dequantise + tensor cores).
+ */
+int coset_e8_vlut_gemv(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
+                       const void* x, int x_dtype, int64_t ldx, int T, const float* bias, float* y,
+                       int64_t ldy, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,77 @@
+"""Code-domain matmul (E8CodeLinear) against decode-then-float32-matmul of the CPU restatement
+of the reference (BASELINE config: weight stored as E8 codes, activations bf16 / float32)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def rel(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30)
+
+
+def make(n_out, n_in, tiling, beta_value=25.0, seed=0):
+    torch.manual_seed(seed)
+    W = torch.randn(n_out, n_in) * 0.02
+    kb = n_in // 8
+    if tiling == "block":
+        beta = torch.full((n_out * kb,), beta_value) * (0.75 + 0.5 * torch.rand(n_out * kb))
+        bpt = 1
+    else:
+        beta = torch.full((n_out,), beta_value) * (0.75 + 0.5 * torch.rand(n_out))
+        bpt = kb
+    digits = O.encode(W.numpy().reshape(-1, 8), beta=beta.numpy(), scale_mode=2, blocks_per_tile=bpt, threads=8)
+    w_hat = O.decode(digits, beta=beta.numpy(), scale_mode=2, blocks_per_tile=bpt, threads=8).reshape(n_out, n_in)
+    return W, beta, bpt, digits, w_hat
+
+
+@pytest.mark.parametrize("tiling", ["block", "row"])
+@pytest.mark.parametrize("T", [1, 3, 16, 40])
+def test_small_t_fp32_activations(tiling, T):
+    from coset_b200.vlut import E8CodeLinear
+    W, beta, bpt, digits, w_hat = make(256, 512, tiling)
+    bias = torch.randn(256)
+    lin = E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt, bias.cuda())
+    assert np.array_equal(lin.codes.cpu().numpy().view(np.uint32).reshape(-1), O.pack_q4(digits))
+    assert np.array_equal(lin.dense_weight().cpu().numpy(), w_hat)  # bit-exact dequantised weight
+    x = torch.randn(T, 512)
+    want = x.double().numpy() @ w_hat.astype(np.float64).T + bias.double().numpy()
+    got = lin(x.cuda()).cpu().numpy()
+    assert rel(got, want) < 1e-5
+
+
+@pytest.mark.parametrize("T", [1, 16, 256])
+def test_bf16_activations_config_shape(T):
+    """BASELINE vLUT config at reduced width for the CPU oracle: beta = 25 (scaled sigma 0.5)."""
+    from coset_b200.vlut import E8CodeLinear
+    W, beta, bpt, digits, w_hat = make(512, 1024, "block")
+    lin = E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt)
+    x = torch.randn(T, 1024).to(torch.bfloat16)
+    want = x.float().numpy() @ w_hat.T
+    got = lin(x.cuda()).float().cpu().numpy()
+    assert rel(got, want) < 1e-2
+
+
+def test_literal_scale_gives_zero_output():
+    from coset_b200.vlut import E8CodeLinear
+    W = torch.randn(64, 128) * 0.02
+    beta = torch.full((64 * 16,), 0.021440971642732620)
+    lin = E8CodeLinear.from_weight(W.cuda(), beta.cuda(), 1)
+    assert not lin.codes.any()
+    assert not lin(torch.randn(4, 128, device="cuda")).any()
+
+
+def test_export_from_trained_layer():
+    from coset_b200.core.e8 import create_e8_hnlq_linear
+    from coset_b200.vlut import E8CodeLinear
+    layer = create_e8_hnlq_linear(128, 64, device="cuda", init_kwargs={"std": 20.0}, weight_clip_value=1e9)
+    lin = E8CodeLinear.from_qat_layer(layer)
+    x = torch.randn(5, 128, device="cuda")
+    with torch.no_grad():
+        assert rel(lin(x).cpu().numpy(), layer(x).cpu().numpy()) < 1e-5
+    with pytest.raises(ValueError):
+        E8CodeLinear.from_weight(torch.zeros(4, 12, device="cuda"), torch.ones(4, device="cuda"), 1)
