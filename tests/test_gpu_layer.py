@@ -118,6 +118,6 @@ def test_bf16_activations(golden_layer):
     y32 = layer(x)
     y16 = layer(x.to(torch.bfloat16))
     assert y16.dtype == torch.bfloat16
-    assert rel(y16.float().cpu().numpy(), y32.detach().cpu().numpy()) < 1e-2
+    assert rel(y16.detach().float().cpu().numpy(), y32.detach().cpu().numpy()) < 1e-2
     y16.float().sum().backward()
     assert layer.weight.grad is not None and layer.theta_beta.grad is not None
