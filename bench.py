@@ -38,8 +38,8 @@ BETA_HEADLINE = 25.0
 BETA_LITERAL = 0.021440971642732620
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one encode launch, from the ncu capture
-# summarised in profiles/ (null until a capture exists for the current kernel).
-ENCODE_TRAFFIC_BYTES_PER_LAUNCH = None
+# summarised in profiles/, scaled to the full launch by the number of blocks.
+ENCODE_TRAFFIC_BYTES_PER_LAUNCH = 1.2756e9  # 8 x (151.15 + 8.30) MB measured on 2^22 blocks, see profiles/codec_q4m2_bulk_fp32.md
 
 
 def make_values(n_values, seed):
@@ -352,7 +352,7 @@ def main():
             "frac_of_hbm_peak": value / world / peak,
             "roofline": {"bound": "hbm", "kernel": "k_encode_q4m2 (dominant: %.0f%% of the step)" % (100 * per[0] / (per[0] + per[1])),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": ENCODE_TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes_per_launch": n * BYTES_PER_BLOCK_ENC,
+                         "traffic": ENCODE_TRAFFIC_BYTES_PER_LAUNCH * n / N_BLOCKS, "algorithmic_bytes_per_launch": n * BYTES_PER_BLOCK_ENC,
                          "peak_source": peak_src, "ms_per_launch": enc_ms,
                          "decode": {"achieved": n * BYTES_PER_BLOCK_DEC / (per[1] * 1e-3) / 1e9, "ms_per_launch": per[1]}},
             "clocks": clocks,

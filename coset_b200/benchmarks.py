@@ -1,0 +1,171 @@
+"""Secondary benchmarks (the reference declares a `coset-benchmark` entry point that does not
+exist, pyproject.toml:67).  One JSON line per measurement:
+
+    python -m coset_b200.benchmarks qat        # E8HNLQLinear QAT step, W [3072, 768], 4096 bf16 tokens
+    python -m coset_b200.benchmarks vlut       # code-domain matmul, W [4096, 4096], T in {1, 16, 256, 4096}
+    python -m torch.distributed.run --nproc-per-node N -m coset_b200.benchmarks gradcomm
+                                               # E8-quantised gradient exchange, BERT-base-shaped gradient
+
+Timing: CUDA events on the current stream, warm-up first, inputs resident on the device.
+Roofline denominators: MEASURED_PEAKS.json at the repository root when present, else the
+fallbacks 6650 GB/s and 1590 TFLOP/s.
+"""
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def cuda_time(fn, iters=20, warmup=5):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def bench_qat():
+    from .core.e8 import create_e8_hnlq_linear
+    from .core.layers import e8_fake_quantize
+    hbm, tf, src = peaks()
+    torch.manual_seed(0)
+    tokens, d_in, d_out = 4096, 768, 3072
+    x = torch.randn(tokens, d_in, device="cuda").to(torch.bfloat16)
+    t = torch.randn(tokens, d_out, device="cuda").to(torch.bfloat16)
+    for tag, std in (("literal std=0.02 (all weights quantise to 0)", 0.02), ("std=20 (55% non-zero weights)", 20.0)):
+        for tiling in ("row", "block"):
+            layer = create_e8_hnlq_linear(d_in, d_out, q=4, M=2, tiling=tiling, init_kwargs={"std": std}, device="cuda")
+
+            def step():
+                layer.zero_grad(set_to_none=True)
+                y = layer(x)
+                ((y - t).float() ** 2).mean().backward()
+
+            ms = cuda_time(step)
+            beta = layer._beta().detach()
+            bpt = layer.blocks_per_row if tiling == "row" else 1
+            w = layer.weight.detach()
+            fq = cuda_time(lambda: e8_fake_quantize(w, beta, bpt, 4, 2.0, torch.bfloat16))
+            n_blocks = w.numel() // 8
+            fq_bytes = n_blocks * (32 + 16 + 4) + beta.numel() * 4  # fp32 in, bf16 out, codes out, scales
+            print(json.dumps({
+                "bench": "qat_step", "weights": tag, "tiling": tiling, "tokens": tokens, "shape": [d_out, d_in],
+                "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3),
+                "gemm_tflops_equiv": 3 * 2 * tokens * d_in * d_out / (ms * 1e-3) / 1e12,
+                "fake_quant_fwd_ms": fq, "fake_quant_fwd_GBps": fq_bytes / (fq * 1e-3) / 1e9,
+                "fake_quant_frac_of_hbm": fq_bytes / (fq * 1e-3) / 1e9 / hbm, "peaks": src}), flush=True)
+
+
+def bench_vlut():
+    from .vlut import E8CodeLinear
+    hbm, tf, src = peaks()
+    torch.manual_seed(0)
+    n = 4096
+    W = (torch.randn(n, n) * 0.02).cuda()
+    for tiling, bpt, nbeta in (("block", 1, n * n // 8), ("row", n // 8, n)):
+        beta = torch.full((nbeta,), 25.0, device="cuda")
+        lin = E8CodeLinear.from_weight(W, beta, bpt, small_t_max=64)
+        wbytes = n * n // 8 * 4 + nbeta * 4
+        for T in (1, 16, 256, 4096):
+            x = torch.randn(T, n, device="cuda").to(torch.bfloat16)
+            lin(x)
+            ms = cuda_time(lambda: lin(x), iters=50 if T <= 256 else 10)
+            flops = 2.0 * T * n * n
+            rec = {"bench": "vlut_matmul", "tiling": tiling, "T": T, "shape": [n, n], "ms": ms,
+                   "tokens_per_s": T / (ms * 1e-3), "path": "code-domain kernel" if T <= 64 else "bf16 dequant + tensor cores",
+                   "peaks": src}
+            if T <= 64:
+                by = wbytes + T * n * 2 + T * n * 4
+                rec.update({"bound": "hbm", "GBps": by / (ms * 1e-3) / 1e9, "frac": by / (ms * 1e-3) / 1e9 / hbm})
+            else:
+                rec.update({"bound": "tensor", "TFLOPs": flops / (ms * 1e-3) / 1e12, "frac": flops / (ms * 1e-3) / 1e12 / tf})
+            print(json.dumps(rec), flush=True)
+
+
+def bench_gradcomm():
+    import torch.distributed as dist
+    from .gradcomm import E8GradientExchange, bert_base_gradient_numel
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    n = bert_base_gradient_numel()
+    g = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    grad = torch.randn(n, device="cuda", generator=g) * 1e-3
+    ex = E8GradientExchange(scale=500.0)
+    out = torch.empty_like(grad)
+
+    def quantised():
+        ex.all_reduce_mean(grad, out=out)
+
+    ref = grad.clone()
+
+    def plain():
+        ref.copy_(grad)
+        if world > 1:
+            dist.all_reduce(ref)
+        ref.div_(world)
+
+    res = {}
+    for name, fn in (("e8_exchange_ms", quantised), ("fp32_allreduce_ms", plain)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / 10], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res[name] = float(t.item())
+    if rank == 0:
+        hbm, _, src = peaks()
+        n_blocks = n // 8
+        hbm_bytes = n_blocks * 36 + world * n_blocks * 4 + n_blocks * 32
+        res.update({"bench": "gradient_exchange", "n_gpus": world, "values": n, "scale": 500.0,
+                    "wire_bytes_sent_per_rank": n_blocks * 4, "wire_bytes_fp32_ring_per_rank": 2 * (world - 1) / max(world, 1) * n * 4,
+                    "gradient_GBps_per_gpu": n * 4 / (res["e8_exchange_ms"] * 1e-3) / 1e9,
+                    "kernel_hbm_bytes": hbm_bytes, "hbm_floor_ms": hbm_bytes / (hbm * 1e9) * 1e3, "peaks": src,
+                    "speedup_vs_fp32_allreduce": res["fp32_allreduce_ms"] / res["e8_exchange_ms"]})
+        print(json.dumps(res), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main(argv=None):
+    argv = sys.argv[1:] if argv is None else argv
+    which = argv[0] if argv else "all"
+    if which in ("qat", "all"):
+        bench_qat()
+    if which in ("vlut", "all"):
+        bench_vlut()
+    if which in ("gradcomm", "all"):
+        bench_gradcomm()
+
+
+if __name__ == "__main__":
+    main()
