@@ -203,6 +203,121 @@ k_encode_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::T
     __stcs(codes + b, e8::encode_q4m2<LITERAL>(v));
 }
 
+// Queued encoder (the production path for q=4, M=2).
+//
+// Warps are persistent and take 32 consecutive blocks per step.  Every lane runs the cheap
+// rint-based level-0 path; whatever that path cannot finish -- a block on a rounding tie, a block
+// whose top level is not the origin, a non-finite block -- is NOT handled in place (that would
+// idle the other 31 lanes for hundreds of instructions) but appended to a per-warp queue in shared
+// memory.  When 32 entries have accumulated (and once at the end) the warp drains the queue
+// with all lanes busy, each lane completing one queued block with the always-valid tiers.
+// In the regime where most blocks need the top level (an overloaded quantiser) the level is run
+// in place instead, so the queue only ever carries the rare cases.
+constexpr int kQueueSlots = 64;   // < 32 left after a drain + at most 32 new per step
+constexpr int kEncWarps = kThreads / 32;
+
+template <int DT, int MODE>
+__global__ void __launch_bounds__(kThreads, 4)
+k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
+                     uint32_t* __restrict__ codes) {
+    __shared__ float q_x[kEncWarps][8][kQueueSlots];
+    __shared__ uint32_t q_meta[kEncWarps][4][kQueueSlots];  // code so far, block index lo / hi, first open level
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t lanes_below = (1u << lane) - 1u;
+    int count = 0;  // warp-uniform number of queued blocks
+    int64_t base = ((int64_t)blockIdx.x * kEncWarps + warp) * 32;
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    bool more = base < n;
+    while (true) {
+        if (more) {
+            const int64_t b = base + lane;
+            const bool active = b < n;
+            float v[8];
+            float s = 1.0f;
+            if (active) {
+                e8::Row8<DT>::load(x, b, v);
+                s = load_scale<MODE>(scale, td, b);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+            }
+            float amax = 0.0f, s1 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[i] = scale_in<MODE>(v[i], s);
+                amax = fmaxf(amax, fabsf(v[i]));
+                s1 += fabsf(v[i]);
+            }
+            const bool finite = (s1 - s1) == 0.0f;
+            uint32_t code = 0;
+            int open_level = 2;  // 2 = finished
+            if (!finite) {
+                open_level = 0;
+            } else if (!(amax <= 0.49f && s1 <= 1.99f)) {
+                if (!e8::level_fast_q4<false>(v, amax, code)) open_level = 0;
+            }
+            // top level: origin unless max|x| > 1.96 or sum|x| > 7.96 (the level sees x / 4)
+            bool need1 = active && open_level == 2 && !(amax <= 1.96f && s1 <= 7.96f);
+            if (__popc(__ballot_sync(0xffffffffu, need1)) >= 12) {
+                if (need1) {
+                    float v1[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v1[i] = __fmul_rn(v[i], 0.25f);
+                    uint32_t d1;
+                    if (e8::level_fast_q4<false>(v1, amax * 0.25f, d1)) code |= d1 << 16; else open_level = 1;
+                }
+            } else if (need1) {
+                open_level = 1;
+            }
+            const bool defer = active && open_level != 2;
+            const uint32_t bal = __ballot_sync(0xffffffffu, defer);
+            if (active && !defer) __stcs(codes + b, code);
+            if (defer) {
+                const int pos = count + __popc(bal & lanes_below);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) q_x[warp][i][pos] = v[i];
+                q_meta[warp][0][pos] = code;
+                q_meta[warp][1][pos] = (uint32_t)b;
+                q_meta[warp][2][pos] = (uint32_t)((uint64_t)b >> 32);
+                q_meta[warp][3][pos] = (uint32_t)open_level;
+            }
+            count += __popc(bal);
+            base += stride;
+            more = base < n;
+        }
+        if (count >= 32 || (!more && count > 0)) {
+            __syncwarp();
+            const int take = count < 32 ? count : 32;
+            if (lane < take) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = q_x[warp][i][lane];
+                uint32_t code = q_meta[warp][0][lane];
+                int64_t b = (int64_t)(((uint64_t)q_meta[warp][2][lane] << 32) | q_meta[warp][1][lane]);
+                int start = (int)q_meta[warp][3][lane];
+                __stcs(codes + b, e8::finish_block_q4(v, code, start));
+            }
+            __syncwarp();
+            const int rem = count - take;
+            if (lane < rem) {  // move the tail (fewer than 32 entries) to the front
+                float t[8];
+                uint32_t u[4];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) t[i] = q_x[warp][i][32 + lane];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) u[i] = q_meta[warp][i][32 + lane];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) q_x[warp][i][lane] = t[i];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) q_meta[warp][i][lane] = u[i];
+            }
+            __syncwarp();
+            count = rem;
+        }
+        if (!more && count == 0) break;
+    }
+}
+
 // Two blocks per thread (kThreads apart, so every access stays coalesced): both codes are
 // loaded before the first table lookup, which doubles the gathers in flight per thread.
 constexpr int kDecPerThread = 2;
@@ -382,7 +497,8 @@ int coset_e8_encode(const void* x, int x_dtype, const float* scale, int scale_mo
     e8::TileDiv td = e8::make_tile_div(scale_mode == COSET_SCALE_MUL_TILE ? blocks_per_tile : 1, n_blocks);
     unsigned grid = grid_for(n_blocks);
     if (q == 4 && M == 2 && sem == COSET_SEM_CORE) {
-        DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2<DT, MODE, false><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes))))
+        unsigned qgrid = grid < (unsigned)(sm_count() * 32) ? grid : (unsigned)(sm_count() * 32);
+        DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2_queued<DT, MODE><<<qgrid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes))))
     } else if (q == 4 && M == 2) {
         DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2<DT, MODE, true><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes))))
     } else if (q <= 4) {

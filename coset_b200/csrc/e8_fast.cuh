@@ -72,23 +72,36 @@ __device__ __forceinline__ void scan_coset(const float (&w)[8], const float (&d)
     s.sumsq = s.odd ? a + c : a;
 }
 
+// kMagic + custom_round(x), evaluated exactly as the reference does (coset/core/base.py:194-202:
+// nudge by eps toward zero, add 0.5, floor); the floor is a round-down add of the magic constant.
+__device__ __forceinline__ float magic_custom_round(float x) {
+    float nudge = __uint_as_float((__float_as_uint(x) & 0x80000000u) | 0x34000000u);  // copysign(2^-23, x)
+    float t = __fadd_rn(__fsub_rn(x, nudge), 0.5f);
+    return __fadd_rd(t, kMagic);
+}
+
 // Returns true and the 16-bit level word when the fast path can answer; amax >= max |x_i|.
+// EXACT_ROUND = false: rint() by one magic add, valid only away from rounding ties (guarded).
+// EXACT_ROUND = true : the reference's custom_round op by op (3 more instructions per
+//   coordinate and coset), valid everywhere, so exact ties -- zeros, integers, half-integers in
+//   the data -- stay on this path; only the distance guard can still refuse.
+template <bool EXACT_ROUND>
 __device__ __forceinline__ bool level_fast_q4(const float (&x)[8], float amax, uint32_t& digits) {
     if (!(amax < 60.0f)) return false;
     float thr = __fmaf_rn(amax + 1.0f, -4.76837158203125e-07f, 0.5f);
     float w[8], d[8], ws[8], ds[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        w[i] = __fadd_rn(x[i], kMagic);
-        d[i] = __fsub_rn(x[i], __fsub_rn(w[i], kMagic));
         float xs = __fsub_rn(x[i], 0.5f);
-        ws[i] = __fadd_rn(xs, kMagic);
+        w[i] = EXACT_ROUND ? magic_custom_round(x[i]) : __fadd_rn(x[i], kMagic);
+        ws[i] = EXACT_ROUND ? magic_custom_round(xs) : __fadd_rn(xs, kMagic);
+        d[i] = __fsub_rn(x[i], __fsub_rn(w[i], kMagic));
         ds[i] = __fsub_rn(xs, __fsub_rn(ws[i], kMagic));
     }
     CosetScan s0, s1;
     scan_coset(w, d, s0);
     scan_coset(ws, ds, s1);
-    if (!(s0.m < thr) || !(s1.m < thr)) return false;
+    if (!EXACT_ROUND && (!(s0.m < thr) || !(s1.m < thr))) return false;
     float delta = s1.sumsq - s0.sumsq;
     if (!(fabsf(delta) > 6.103515625e-05f)) return false;
     bool half = delta < 0.0f;  // the D8 + 1/2 candidate is strictly closer
@@ -115,15 +128,55 @@ __device__ __forceinline__ bool level_fast_q4(const float (&x)[8], float amax, u
     return true;
 }
 
-// One level, always exact: the fast path when it can prove its answer, else the literal search.
-__device__ __forceinline__ uint32_t level_q4(const float (&x)[8], float amax) {
+// Second and third attempt, out of line (rare): exact-rounding fast path, then the literal search.
+static __device__ __noinline__ uint32_t level_slow_q4(const float (&x)[8], float amax) {
     uint32_t digits;
-    if (level_fast_q4(x, amax, digits)) return digits;
+    if (level_fast_q4<true>(x, amax, digits)) return digits;
     float y[8];
     int dg[8];
     bool half = projection(x, y);
     encode_coords(y, half, 4, dg);
     return pack_level<2>(dg);
+}
+
+// One level, always exact: the cheapest path that can prove its answer.
+__device__ __forceinline__ uint32_t level_q4(const float (&x)[8], float amax) {
+    uint32_t digits;
+    if (level_fast_q4<false>(x, amax, digits)) return digits;
+    return level_slow_q4(x, amax);
+}
+
+// Completes a block whose levels `start`..1 are still open, using the tiers that accept every
+// input (exact-rounding fast path, then the literal search).  x holds the level-0 (scaled) input.
+// Used for the deferred, warp-compacted work of the queued encoder.
+__device__ __forceinline__ uint32_t finish_block_q4(float (&x)[8], uint32_t code, int start) {
+    float amax = 0.0f, s1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        amax = fmaxf(amax, fabsf(x[i]));
+        s1 += fabsf(x[i]);
+    }
+    bool finite = (s1 - s1) == 0.0f;
+#pragma unroll 1
+    for (int m = 0; m < 2; ++m) {
+        bool origin = finite && amax <= 0.49f && s1 <= 1.99f;
+        if (m >= start && !origin) {
+            uint32_t digits;
+            if (!level_fast_q4<true>(x, finite ? amax : __int_as_float(0x7fc00000), digits)) {
+                float y[8];
+                int dg[8];
+                bool half = projection(x, y);
+                encode_coords(y, half, 4, dg);
+                digits = pack_level<2>(dg);
+            }
+            code |= digits << (16 * m);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], 0.25f);
+        amax *= 0.25f;
+        s1 *= 0.25f;
+    }
+    return code;
 }
 
 // Both levels of e8_encode for q = 4 (coset/core/e8/codecs.py:75-81).  x / 4 is exact in
