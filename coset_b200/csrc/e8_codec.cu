@@ -287,7 +287,7 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
         }
         if (count >= 32 || (!more && count > 0)) {
             __syncwarp();
-            const int take = count < 32 ? count : 32;
+            const int take = count < 32 ? count : 16;
             if (lane < take) {
                 float v[8];
 #pragma unroll
@@ -497,7 +497,8 @@ int coset_e8_encode(const void* x, int x_dtype, const float* scale, int scale_mo
     e8::TileDiv td = e8::make_tile_div(scale_mode == COSET_SCALE_MUL_TILE ? blocks_per_tile : 1, n_blocks);
     unsigned grid = grid_for(n_blocks);
     if (q == 4 && M == 2 && sem == COSET_SEM_CORE) {
-        unsigned qgrid = grid < (unsigned)(sm_count() * 32) ? grid : (unsigned)(sm_count() * 32);
+        // persistent warps: 16 CTAs per SM worth of grid (4 resident at a time) balances queue fill and tail
+        unsigned qgrid = grid < (unsigned)(sm_count() * 16) ? grid : (unsigned)(sm_count() * 16);
         DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2_queued<DT, MODE><<<qgrid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes))))
     } else if (q == 4 && M == 2) {
         DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2<DT, MODE, true><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes))))
