@@ -36,6 +36,8 @@ SIGNATURES = {
     "coset_e8_decode_host": [_vp, _vp, _vp, _i32, _i64, _i64, _i32, _i32, _vp, _i32],
     "coset_e8_decode_mean": [_vp, _i32, _i64, _i64, _f32, _vp, _i32, _vp],
     "coset_e8_vlut_gemv": [_vp, _vp, _i64, _i32, _i32, _vp, _i32, _i64, _i32, _vp, _vp, _i64, _vp],
+    "coset_e8_quant_stats_scratch_bytes": [_i64],
+    "coset_e8_quant_stats": [_vp, _i32, _vp, _i32, _i64, _i64, _vp, _i64, _vp, _vp],
     "coset_e8_fake_quant_bwd": [_vp, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _vp, _vp],
 }
 
@@ -52,7 +54,8 @@ def lib():
         for name, argtypes in SIGNATURES.items():
             fn = getattr(L, name)
             fn.argtypes = argtypes
-            fn.restype = ctypes.c_char_p if name == "coset_last_error_string" else ctypes.c_int
+            fn.restype = (ctypes.c_char_p if name == "coset_last_error_string"
+                          else ctypes.c_int64 if name.endswith("_scratch_bytes") else ctypes.c_int)
         _lib = L
     return _lib
 

@@ -22,6 +22,7 @@ SOURCES = [
     "e8_host.cu",
     "e8_gradcomm.cu",
     "e8_vlut.cu",
+    "e8_stats.cu",
 ]
 
 NVCC_FLAGS = [

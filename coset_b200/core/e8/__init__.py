@@ -6,6 +6,7 @@ from .codecs import (
     e8_quantize,
     e8_encode_packed,
     e8_decode_packed,
+    e8_quant_stats,
     E8Decoder,
     DecodingMethod,
 )
@@ -18,6 +19,7 @@ __all__ = [
     "e8_quantize",
     "e8_encode_packed",
     "e8_decode_packed",
+    "e8_quant_stats",
     "E8Decoder",
     "DecodingMethod",
     "create_e8_hnlq_linear",

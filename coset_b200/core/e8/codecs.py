@@ -187,3 +187,24 @@ def e8_quantize(x: torch.Tensor, q: int, lattice: Optional[E8Lattice] = None) ->
                                           1, q, 2, 0.0, _lib.ptr(out), _lib.DTYPE_F32, None, _lib.stream())
     _lib.check(rc, "coset_e8_quantize")
     return out.squeeze(0) if squeeze else out
+
+
+def e8_quant_stats(x: torch.Tensor, scale=None, scale_mode: int = _lib.SCALE_NONE, blocks_per_tile: int = 1) -> dict:
+    """Quantisation statistics of the q=4, M=2 codec over x [N, 8] in one pass: squared error and
+    signal energy (scaled domain), overloaded blocks (the overload test of ref/hnlq.py:341 with
+    the core search) and blocks with a non-zero code."""
+    x2, _ = _as_blocks(x)
+    n = x2.shape[0]
+    scale_t, mode, bpt = _scale_args(scale, scale_mode, n, blocks_per_tile, x2.device)
+    lib = _lib.lib()
+    nbytes = lib.coset_e8_quant_stats_scratch_bytes(n)
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x2.device)
+    out = torch.empty(4, dtype=torch.float64, device=x2.device)
+    with torch.cuda.device(x2.device):
+        rc = lib.coset_e8_quant_stats(_lib.ptr(x2), _lib.dtype_code(x2, "x"), _lib.ptr(scale_t), mode, n, bpt,
+                                      _lib.ptr(scratch), nbytes, _lib.ptr(out), _lib.stream())
+    _lib.check(rc, "coset_e8_quant_stats")
+    err2, overload, nonzero, sig2 = out.tolist()
+    return {"squared_error": err2, "signal_energy": sig2, "overloaded_blocks": int(overload),
+            "nonzero_blocks": int(nonzero), "n_blocks": n,
+            "sqnr_db": float("inf") if err2 == 0 else 10.0 * __import__("math").log10(max(sig2, 1e-300) / err2)}

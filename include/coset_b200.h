@@ -174,6 +174,19 @@ int coset_e8_vlut_gemv(const void* codes, const float* beta, int64_t blocks_per_
                        const void* x, int x_dtype, int64_t ldx, int T, const float* bias, float* y,
                        int64_t ldy, void* stream);
 
+/*
+ * Quantisation statistics of the q=4, M=2 codec over a tensor (one pass, deterministic):
+ *   out[0] = sum ||x_hat - x_s||^2   out[1] = overloaded blocks (projection(x_s / q^M) != 0, the
+ *   overload test of ref/hnlq.py:341 / pub/main.tex:878-934)   out[2] = blocks with a non-zero code
+ *   out[3] = sum ||x_s||^2           (x_s = scaled input, x_hat = decode(encode(x_s)), unscaled)
+ * `scratch` is device memory of coset_e8_quant_stats_scratch_bytes(n_blocks) bytes (16-byte
+ * aligned) holding one partial record per CTA; `out` is 4 doubles in device memory.
+ */
+int64_t coset_e8_quant_stats_scratch_bytes(int64_t n_blocks);
+int coset_e8_quant_stats(const void* x, int x_dtype, const float* scale, int scale_mode, int64_t n_blocks,
+                         int64_t blocks_per_tile, void* scratch, int64_t scratch_bytes, double* out,
+                         void* stream);
+
 #ifdef __cplusplus
 }
 #endif
