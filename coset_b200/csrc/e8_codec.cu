@@ -287,7 +287,7 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
         }
         if (count >= 32 || (!more && count > 0)) {
             __syncwarp();
-            const int take = count < 32 ? count : 16;
+            const int take = count < 32 ? count : 32;
             if (lane < take) {
                 float v[8];
 #pragma unroll
