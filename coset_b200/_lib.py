@@ -38,6 +38,8 @@ SIGNATURES = {
     "coset_e8_vlut_gemv": [_vp, _vp, _i64, _i32, _i32, _vp, _i32, _i64, _i32, _vp, _vp, _i64, _vp],
     "coset_e8_quant_stats_scratch_bytes": [_i64],
     "coset_e8_quant_stats": [_vp, _i32, _vp, _i32, _i64, _i64, _vp, _i64, _vp, _vp],
+    "coset_e8_quant_stats_static_max_blocks": [],
+    "coset_e8_quant_stats_static": [_vp, _i32, _vp, _i32, _i64, _i64, _vp, _vp],
     "coset_e8_fake_quant_bwd": [_vp, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _vp, _vp],
 }
 
@@ -55,7 +57,7 @@ def lib():
             fn = getattr(L, name)
             fn.argtypes = argtypes
             fn.restype = (ctypes.c_char_p if name == "coset_last_error_string"
-                          else ctypes.c_int64 if name.endswith("_scratch_bytes") else ctypes.c_int)
+                          else ctypes.c_int64 if name.endswith(("_scratch_bytes", "_max_blocks")) else ctypes.c_int)
         _lib = L
     return _lib
 

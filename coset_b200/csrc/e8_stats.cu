@@ -7,6 +7,8 @@
 //
 // Two stages, deterministic (no atomics): every CTA reduces its blocks to one partial record in
 // SCRATCH memory, then a single CTA folds the partial records in a fixed order.
+#include <mutex>
+
 #include "common.cuh"
 #include "e8_fast.cuh"
 #include "e8_io.cuh"
@@ -24,7 +26,19 @@ struct Partial {
     unsigned long long overload, nonzero;
 };
 
-template <int DT, int MODE>
+// twice the reconstruction from the code without the residual table (literal decoder per level)
+__device__ __forceinline__ void decode_twice_literal(uint32_t code, float (&v2)[8]) {
+    int d0[8], d1[8];
+    float r0[8], r1[8];
+    e8::unpack_level<2>(code & 0xffffu, d0);
+    e8::unpack_level<2>(code >> 16, d1);
+    e8::level_residual(d0, 4.0f, r0);
+    e8::level_residual(d1, 4.0f, r1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v2[i] = __fmul_rn(__fadd_rn(r0[i], __fmul_rn(4.0f, r1[i])), 2.0f);
+}
+
+template <int DT, int MODE, bool USE_TABLE = true>
 __global__ void __launch_bounds__(kThreads)
 k_stats_partial(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
                 const uint2* __restrict__ table, Partial* __restrict__ partials) {
@@ -48,7 +62,7 @@ k_stats_partial(const void* __restrict__ x, const float* __restrict__ scale, e8:
             s1 += fabsf(v[i]);
         }
         uint32_t code = e8::encode_q4m2<false>(v);  // leaves v = x_s / 16
-        e8::decode_q4m2_twice(code, table, v2);
+        if (USE_TABLE) e8::decode_q4m2_twice(code, table, v2); else decode_twice_literal(code, v2);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             float d = __fmaf_rn(v2[i], 0.5f, -xs[i]);
@@ -107,13 +121,17 @@ __global__ void __launch_bounds__(kThreads) k_stats_final(const Partial* __restr
     }
 }
 
+template <bool USE_TABLE>
 int launch_stats(const void* x, int x_dtype, const float* scale, int scale_mode, int64_t n_blocks, int64_t blocks_per_tile,
                  Partial* partials, double* out, cudaStream_t st) {
-    const uint2* table = residual_table_q4(st);
-    if (!table) return COSET_E_STATE;
+    const uint2* table = nullptr;
+    if (USE_TABLE) {
+        table = residual_table_q4(st);
+        if (!table) return COSET_E_STATE;
+    }
     e8::TileDiv td = e8::make_tile_div(scale_mode == COSET_SCALE_MUL_TILE ? blocks_per_tile : 1, n_blocks);
     int ctas = (int)((n_blocks + kBlocksPerCta - 1) / kBlocksPerCta);
-#define STATS_CASE(DT, MODE) k_stats_partial<DT, MODE><<<ctas, kThreads, 0, st>>>(x, scale, td, n_blocks, table, partials)
+#define STATS_CASE(DT, MODE) k_stats_partial<DT, MODE, USE_TABLE><<<ctas, kThreads, 0, st>>>(x, scale, td, n_blocks, table, partials)
     if (x_dtype == COSET_DTYPE_F32) {
         if (scale_mode == 0) STATS_CASE(0, 0); else if (scale_mode == 1) STATS_CASE(0, 1); else STATS_CASE(0, 2);
     } else {
@@ -135,9 +153,46 @@ int check_stats_args(const void* x, int x_dtype, const float* scale, int scale_m
     return 0;
 }
 
+// ---- scratch for callers that cannot allocate -------------------------------------------------
+// One partial record per CTA, for at most kStaticMaxCtas CTAs (2^25 blocks).  The array lives in
+// every GPU that loads the library until the process exits (128 KB).
+constexpr int kStaticMaxCtas = 4096;
+static __device__ __align__(256) unsigned char g_stats_scratch[kStaticMaxCtas * sizeof(Partial)];
+
+// Device address of g_stats_scratch on the CURRENT device.  In host code the symbol's name is only
+// a stand-in, not a device pointer, so the address is asked from the runtime once per device.
+Partial* static_scratch_of_current_device() {
+    static std::mutex mu;
+    static Partial* addr[64] = {nullptr};
+    int dev = 0;
+    if (check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return nullptr;
+    if (dev < 0 || dev >= 64) { fail(COSET_E_STATE, "device index %d out of range", dev); return nullptr; }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[dev]) {
+        void* p = nullptr;
+        if (check_cuda(cudaGetSymbolAddress(&p, g_stats_scratch), "cudaGetSymbolAddress(g_stats_scratch)")) return nullptr;
+        addr[dev] = (Partial*)p;
+    }
+    return addr[dev];
+}
+
 }  // namespace
 
 extern "C" {
+
+int64_t coset_e8_quant_stats_static_max_blocks(void) { return (int64_t)kStaticMaxCtas * kBlocksPerCta; }
+
+int coset_e8_quant_stats_static(const void* x, int x_dtype, const float* scale, int scale_mode, int64_t n_blocks,
+                                int64_t blocks_per_tile, double* out, void* stream) {
+    if (int e = check_stats_args(x, x_dtype, scale, scale_mode, n_blocks, blocks_per_tile, out)) return e;
+    if (n_blocks > coset_e8_quant_stats_static_max_blocks())
+        return fail(COSET_E_UNSUPPORTED, "n_blocks = %lld exceeds the %lld blocks the built-in scratch array covers; "
+                    "split the tensor or use coset_e8_quant_stats with caller-provided scratch",
+                    (long long)n_blocks, (long long)coset_e8_quant_stats_static_max_blocks());
+    Partial* scratch = static_scratch_of_current_device();
+    if (!scratch) return COSET_E_STATE;
+    return launch_stats<false>(x, x_dtype, scale, scale_mode, n_blocks, blocks_per_tile, scratch, out, (cudaStream_t)stream);
+}
 
 int64_t coset_e8_quant_stats_scratch_bytes(int64_t n_blocks) {
     if (n_blocks < 1) return 0;
@@ -149,7 +204,7 @@ int coset_e8_quant_stats(const void* x, int x_dtype, const float* scale, int sca
     if (int e = check_stats_args(x, x_dtype, scale, scale_mode, n_blocks, blocks_per_tile, out)) return e;
     if (!scratch || scratch_bytes < coset_e8_quant_stats_scratch_bytes(n_blocks) || !aligned(scratch, 16))
         return fail(COSET_E_BADARG, "scratch must be 16-byte aligned and hold coset_e8_quant_stats_scratch_bytes(n_blocks) bytes");
-    return launch_stats(x, x_dtype, scale, scale_mode, n_blocks, blocks_per_tile, (Partial*)scratch, out, (cudaStream_t)stream);
+    return launch_stats<true>(x, x_dtype, scale, scale_mode, n_blocks, blocks_per_tile, (Partial*)scratch, out, (cudaStream_t)stream);
 }
 
 }  // extern "C"

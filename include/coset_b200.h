@@ -187,6 +187,28 @@ int coset_e8_quant_stats(const void* x, int x_dtype, const float* scale, int sca
                          int64_t blocks_per_tile, void* scratch, int64_t scratch_bytes, double* out,
                          void* stream);
 
+/*
+ * coset_e8_quant_stats for callers that must not allocate device memory.  (No counterpart in the
+ * reference.)  Some hosts of this library run where cudaMalloc is off limits -- inside another
+ * framework's memory pool with a fixed budget, in a plugin that is handed only its input and
+ * output buffers, or on a thread that may not take the allocator's lock -- and those callers have
+ * nowhere to get the scratch buffer the regular entry point asks for.  This variant keeps the
+ * per-CTA partial records in a 128 KB array that is part of the library image on every GPU that
+ * loads it, and reconstructs without the (allocated) residual table.  Same arguments and results
+ * as coset_e8_quant_stats, minus the scratch pointer.
+ *   - n_blocks above coset_e8_quant_stats_static_max_blocks() (2^25) is refused with
+ *     COSET_E_UNSUPPORTED; nothing is launched.
+ *   - The first call on each device looks up the array's device address (no allocation); make
+ *     that first call before any stream capture begins on that device.
+ *   - All calls on a device share the one array.  Every launch overwrites the records it reads,
+ *     so nothing needs clearing between calls, but two calls whose kernels overlap on the GPU
+ *     (different streams) race on it: serialise them.
+ *   - Calls no cudaMalloc / cudaFree or any allocating library routine.
+ */
+int64_t coset_e8_quant_stats_static_max_blocks(void);
+int coset_e8_quant_stats_static(const void* x, int x_dtype, const float* scale, int scale_mode,
+                                int64_t n_blocks, int64_t blocks_per_tile, double* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
