@@ -23,6 +23,7 @@ SOURCES = [
     "e8_gradcomm.cu",
     "e8_vlut.cu",
     "e8_stats.cu",
+    "e8_ref.cu",
 ]
 
 NVCC_FLAGS = [

@@ -33,7 +33,8 @@
  *                   every block runs the op-by-op restatement, none the guarded fast path; the
  *                   tests use it to cross-check the fast path on inputs too large for the CPU oracle
  *   COSET_SEM_REF   bit-exact with ref/hnlq.py (float64, tie dither, re-quantising recurrence,
- *                   overload loop); parity-only, not a timed path
+ *                   overload loop); parity-only, not a timed path; served by its own entry points
+ *                   coset_e8_ref_encode / coset_e8_ref_decode (it needs float64 data and a T output)
  *
  * Exactness domain of COSET_SEM_CORE: finite inputs with |scaled x| <= 2^20.  Outside it the
  * call still succeeds and never faults, but the digits are unspecified.
@@ -208,6 +209,21 @@ int coset_e8_quant_stats(const void* x, int x_dtype, const float* scale, int sca
 int64_t coset_e8_quant_stats_static_max_blocks(void);
 int coset_e8_quant_stats_static(const void* x, int x_dtype, const float* scale, int scale_mode,
                                 int64_t n_blocks, int64_t blocks_per_tile, double* out, void* stream);
+
+/*
+ * COSET_SEM_REF: the paper-faithful quantiser ref/hnlq.py (HNLQ.encode, ref/hnlq.py:304-383;
+ * HNLQ.decode, ref/hnlq.py:389-445; closest_point_E8 / g_x / custom_round, ref/utils.py:371-537) in
+ * float64.  Parity-only.  x, out: [n_blocks, 8] float64; digits: [n_blocks, M, 8] int32;
+ * T: [n_blocks] int32 (overload halvings).  dither_host: the 8 float64 added before every
+ * closest-point call (the tie dither of ref/utils.py:309-324, or 8 copies of eps when the
+ * reference runs with with_tie_dither=False), read on the host.
+ */
+int coset_e8_ref_encode(const double* x, int64_t n_blocks, double beta, double alpha, int q, int M,
+                        int overload, int max_iter, const double* dither_host, int32_t* digits,
+                        int32_t* T, void* stream);
+int coset_e8_ref_decode(const int32_t* digits, const int32_t* T, int64_t n_blocks, double beta,
+                        double alpha, int q, int M, const double* dither_host, double* out,
+                        void* stream);
 
 #ifdef __cplusplus
 }

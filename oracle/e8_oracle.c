@@ -312,3 +312,123 @@ void e8o_decode_mt(const float* codes, int64_t n, const float* beta, int scale_m
                    int64_t blocks_per_tile, int q, int M, float* xhat, int threads) {
     e8o_run_mt(1, codes, n, beta, scale_mode, blocks_per_tile, q, M, xhat, threads);
 }
+
+/* =============================================================================================
+ * "ref" semantics: the paper-faithful per-vector quantiser ref/hnlq.py (numpy, float64).
+ * Differences from the core codec, all reproduced here: correct g_x flip rule
+ * (ref/utils.py:415-455), a constant tie-dither vector added before EVERY closest-point call
+ * (ref/hnlq.py:173-179, ref/utils.py:309-324), re-quantising recurrence x_l <- Q(x_l) before the
+ * digits and the division (ref/hnlq.py:335-339), digits custom_round(mod(G^-1 x, q))
+ * (ref/hnlq.py:337), overload loop x <- x / 2^alpha (ref/hnlq.py:369-379), reconstruction scaled
+ * by 2^(alpha T) (ref/hnlq.py:445).  Parity: pinned by tests/golden/ref_mode.npz.
+ * ============================================================================================= */
+static double r_custom_round(double x) { /* ref/utils.py:371-412 with float64 eps */
+    const double eps = 2.220446049250313e-16;
+    double s = (x > 0.0) ? 1.0 : ((x < 0.0) ? -1.0 : x * 0.0);
+    double y = x - s * eps;
+    return floor(y + 0.5);
+}
+
+static void r_g_x(const double* x, double* out) { /* ref/utils.py:415-455 */
+    double f[8], best = -1.0;
+    int k = 0;
+    for (int i = 0; i < 8; ++i) {
+        f[i] = r_custom_round(x[i]);
+        out[i] = f[i];
+        double dlt = fabs(x[i] - f[i]);
+        if (dlt > best) { best = dlt; k = i; }
+    }
+    if (x[k] >= 0.0) out[k] = (f[k] < x[k]) ? f[k] + 1.0 : f[k] - 1.0;
+    else out[k] = (f[k] <= x[k]) ? f[k] + 1.0 : f[k] - 1.0;
+}
+
+static double r_fmod_floor(double a, double m) {
+    double r = fmod(a, m);
+    if (r != 0.0 && ((r < 0.0) != (m < 0.0))) r += m;
+    return r;
+}
+
+static void r_closest_e8(const double* x, double* out) { /* ref/utils.py:494-537 */
+    double f0[8], g0[8], xs[8], f1[8], g1[8], y0[8], y1[8], s0 = 0.0, s1 = 0.0, d0 = 0.0, d1 = 0.0;
+    for (int i = 0; i < 8; ++i) { f0[i] = r_custom_round(x[i]); s0 += f0[i]; }
+    r_g_x(x, g0);
+    int e0 = r_fmod_floor(s0, 2.0) == 0.0;
+    for (int i = 0; i < 8; ++i) { xs[i] = x[i] - 0.5; f1[i] = r_custom_round(xs[i]); s1 += f1[i]; }
+    r_g_x(xs, g1);
+    int e1 = r_fmod_floor(s1, 2.0) == 0.0;
+    for (int i = 0; i < 8; ++i) {
+        y0[i] = e0 ? f0[i] : g0[i];
+        y1[i] = (e1 ? f1[i] : g1[i]) + 0.5;
+        d0 += (x[i] - y0[i]) * (x[i] - y0[i]);
+        d1 += (x[i] - y1[i]) * (x[i] - y1[i]);
+    }
+    int c0 = sqrt(d0) < sqrt(d1);
+    for (int i = 0; i < 8; ++i) out[i] = c0 ? y0[i] : y1[i];
+}
+
+static void r_qnn(const double* x, const double* dither, double* out) { /* ref/hnlq.py:179 */
+    double t[8];
+    for (int i = 0; i < 8; ++i) t[i] = x[i] + dither[i];
+    r_closest_e8(t, out);
+}
+
+static int r_encode_once(const double* x, double beta, int q, int M, const double* dither, int32_t* digits) {
+    double xl[8], p[8];
+    for (int i = 0; i < 8; ++i) xl[i] = x[i] / beta;
+    for (int m = 0; m < M; ++m) { /* ref/hnlq.py:335-339 */
+        r_qnn(xl, dither, p);
+        for (int j = 0; j < 8; ++j) {
+            double acc = 0.0;
+            for (int i = 0; i < 8; ++i) acc += (double)GINV[j][i] * p[i];
+            digits[m * 8 + j] = (int32_t)r_custom_round(r_fmod_floor(acc, (double)q));
+        }
+        for (int i = 0; i < 8; ++i) xl[i] = p[i] / (double)q;
+    }
+    r_qnn(xl, dither, p); /* overload test, ref/hnlq.py:341: not allclose(Q(x_l), 0, atol=1e-8) */
+    int over = 0;
+    for (int i = 0; i < 8; ++i) over |= !(fabs(p[i]) <= 1e-8);
+    return over;
+}
+
+/* HNLQ.encode (ref/hnlq.py:344-383). x: [n][8] float64; digits: [n][M][8]; T: [n]. */
+void e8o_ref_encode(const double* x, int64_t n, double beta, double alpha, int q, int M, int overload,
+                    int max_iter, const double* dither, int32_t* digits, int32_t* T) {
+    double scale = pow(2.0, alpha);
+    for (int64_t b = 0; b < n; ++b) {
+        double xv[8];
+        for (int i = 0; i < 8; ++i) xv[i] = x[b * 8 + i];
+        int32_t* dg = digits + b * M * 8;
+        int over = r_encode_once(xv, beta, q, M, dither, dg);
+        int t = 0;
+        if (overload) {
+            while (over && t < max_iter) {
+                t += 1;
+                for (int i = 0; i < 8; ++i) xv[i] = xv[i] / scale;
+                over = r_encode_once(xv, beta, q, M, dither, dg);
+            }
+        }
+        T[b] = t;
+    }
+}
+
+/* HNLQ.decode (ref/hnlq.py:389-445). out: [n][8] float64. */
+void e8o_ref_decode(const int32_t* digits, const int32_t* T, int64_t n, double beta, double alpha, int q, int M,
+                    const double* dither, double* out) {
+    for (int64_t b = 0; b < n; ++b) {
+        double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, w = 1.0;
+        for (int m = 0; m < M; ++m) {
+            double gb[8], s[8], pr[8];
+            for (int j = 0; j < 8; ++j) {
+                double a = 0.0;
+                for (int i = 0; i < 8; ++i) a += (double)G[j][i] * (double)digits[(b * M + m) * 8 + i];
+                gb[j] = a;
+                s[j] = a / (double)q;
+            }
+            r_qnn(s, dither, pr);
+            for (int j = 0; j < 8; ++j) acc[j] = acc[j] + w * (gb[j] - (double)q * pr[j]);
+            w *= (double)q;
+        }
+        double up = pow(2.0, alpha * (double)T[b]);
+        for (int j = 0; j < 8; ++j) out[b * 8 + j] = (beta * acc[j]) * up;
+    }
+}

@@ -145,3 +145,37 @@ def pack_q4(codes):
 def codes_to_int(codes):
     """Reference digits are float32 and may be -0.0; compare them as integers."""
     return np.asarray(codes).astype(np.int64)
+
+
+# ---- "ref" semantics (ref/hnlq.py, float64) ------------------------------------------------
+# Tie-dither vector of ref/utils.py:309-324 for d = 8 (values produced by the reference itself).
+TIE_DITHER = np.array([float.fromhex(h) for h in (
+    "-0x1.254ab98a68347p-44", "0x1.8cacb9e24bcfep-43", "-0x1.c32c65ece7921p-43", "0x1.f24daf0aef791p-44",
+    "-0x1.3977980135725p-43", "0x1.68dd78c4ef9e4p-44", "-0x1.422329c1bb29ap-42", "-0x1.e267a62230fccp-44")])
+
+_f64p = ctypes.POINTER(ctypes.c_double)
+_i32p = ctypes.POINTER(ctypes.c_int32)
+
+
+def ref_encode(x, beta=1.0, alpha=1.0, q=4, M=2, overload=True, max_iter=10, dither=None):
+    """-> (digits int32 [n, M, 8], T int32 [n]) as ref.hnlq.HNLQ.encode yields per vector."""
+    x = np.ascontiguousarray(x, dtype=np.float64)
+    n = x.shape[0]
+    d = np.ascontiguousarray(TIE_DITHER if dither is None else dither, dtype=np.float64)
+    digits = np.empty((n, M, 8), np.int32)
+    T = np.empty(n, np.int32)
+    lib().e8o_ref_encode(x.ctypes.data_as(_f64p), ctypes.c_int64(n), ctypes.c_double(beta), ctypes.c_double(alpha), q, M,
+                         int(bool(overload)), max_iter, d.ctypes.data_as(_f64p), digits.ctypes.data_as(_i32p),
+                         T.ctypes.data_as(_i32p))
+    return digits, T
+
+
+def ref_decode(digits, T, beta=1.0, alpha=1.0, q=4, dither=None):
+    digits = np.ascontiguousarray(digits, dtype=np.int32)
+    T = np.ascontiguousarray(T, dtype=np.int32)
+    n, M, _ = digits.shape
+    d = np.ascontiguousarray(TIE_DITHER if dither is None else dither, dtype=np.float64)
+    out = np.empty((n, 8), np.float64)
+    lib().e8o_ref_decode(digits.ctypes.data_as(_i32p), T.ctypes.data_as(_i32p), ctypes.c_int64(n), ctypes.c_double(beta),
+                         ctypes.c_double(alpha), q, M, d.ctypes.data_as(_f64p), out.ctypes.data_as(_f64p))
+    return out
