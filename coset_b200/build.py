@@ -24,6 +24,7 @@ SOURCES = [
     "e8_vlut.cu",
     "e8_stats.cu",
     "e8_ref.cu",
+    "e8_dequant_gemm.cu",
 ]
 
 NVCC_FLAGS = [

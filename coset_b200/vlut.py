@@ -44,16 +44,50 @@ def e8_vlut_matmul(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_per
     return y
 
 
+def e8_dequant_gemm(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_per_tile: int, x: torch.Tensor,
+                    bias: Optional[torch.Tensor] = None, check: bool = False) -> torch.Tensor:
+    """Same product as e8_vlut_matmul for many tokens, on the tcgen05 tensor cores: weight tiles are
+    decoded to bf16 in shared memory and never written to HBM.  x: bf16 [T, n_in], n_in % 64 == 0.
+    check=True synchronises and raises if a bounded barrier wait expired inside the kernel."""
+    _lib.require_cuda(codes, "codes")
+    _lib.require_cuda(x, "x")
+    if x.dtype != torch.bfloat16:
+        raise TypeError("e8_dequant_gemm takes bfloat16 activations")
+    if codes.dtype != torch.int32 or codes.dim() != 2 or not codes.is_contiguous():
+        raise ValueError("codes must be a contiguous int32 tensor [n_out, n_in / 8]")
+    n_out, kb = codes.shape
+    if x.dim() != 2 or x.shape[1] != kb * 8 or (kb * 8) % 64:
+        raise ValueError(f"x must be [T, {kb * 8}] with n_in a multiple of 64, got {tuple(x.shape)}")
+    x = x.contiguous()
+    T = x.shape[0]
+    y = torch.empty((T, n_out), dtype=torch.float32, device=x.device)
+    status = torch.zeros(1, dtype=torch.int32, device=x.device)
+    b = beta.to(torch.float32).contiguous().view(-1) if beta is not None else None
+    bias32 = bias.to(torch.float32).contiguous() if bias is not None else None
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().coset_e8_dequant_gemm(_lib.ptr(codes), _lib.ptr(b) if b is not None else None,
+                                              int(blocks_per_tile), n_out, kb * 8, _lib.ptr(x), x.stride(0), T,
+                                              _lib.ptr(bias32) if bias32 is not None else None, _lib.ptr(y),
+                                              y.stride(0), _lib.ptr(status), _lib.stream())
+    _lib.check(rc, "coset_e8_dequant_gemm")
+    if check and int(status.item()) != 0:
+        raise RuntimeError("coset_e8_dequant_gemm: a barrier wait expired inside the kernel; the result is invalid")
+    return y
+
+
 class E8CodeLinear(nn.Module):
     """Linear layer that owns E8 codes + scales instead of a dense weight (inference only)."""
 
     def __init__(self, codes: torch.Tensor, beta: torch.Tensor, blocks_per_tile: int,
-                 bias: Optional[torch.Tensor] = None, small_t_max: int = 64):
+                 bias: Optional[torch.Tensor] = None, small_t_max: int = 64, large_t_path: str = "cublas"):
         super().__init__()
         self.out_features, kb = codes.shape
         self.in_features = kb * 8
         self.blocks_per_tile = int(blocks_per_tile)
         self.small_t_max = small_t_max
+        if large_t_path not in ("cublas", "tcgen05"):
+            raise ValueError("large_t_path must be 'cublas' (dequantise once + library GEMM) or 'tcgen05' (fused kernel)")
+        self.large_t_path = large_t_path
         self.register_buffer("codes", codes.contiguous())
         self.register_buffer("beta", beta.to(torch.float32).contiguous().view(-1))
         self.register_buffer("bias", bias.detach().clone() if bias is not None else None)
@@ -98,6 +132,8 @@ class E8CodeLinear(nn.Module):
         else:
             if x2.dtype == torch.float32:
                 y = torch.nn.functional.linear(x2, self.dense_weight(torch.float32), self.bias)
+            elif self.large_t_path == "tcgen05" and x2.dtype == torch.bfloat16 and self.in_features % 64 == 0:
+                y = e8_dequant_gemm(self.codes, self.beta, self.blocks_per_tile, x2, self.bias).to(x2.dtype)
             else:
                 if self._dense is None:
                     self._dense = self.dense_weight(torch.bfloat16)

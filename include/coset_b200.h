@@ -225,6 +225,19 @@ int coset_e8_ref_decode(const int32_t* digits, const int32_t* T, int64_t n_block
                         double alpha, int q, int M, const double* dither_host, double* out,
                         void* stream);
 
+/*
+ * Code-domain product for MANY tokens on the tcgen05 tensor cores: same result as
+ * coset_e8_vlut_gemv (y = x * (decode(codes)/beta)^T + bias) with the weight tile decoded to bf16
+ * in shared memory and multiplied by tcgen05.mma with the accumulator in tensor memory.
+ *   x_bf16: [T, ldx] bf16, n_in a multiple of 64, ldx a multiple of 8;  y: [T, ldy] float32
+ *   status: optional device int, set to 1 if a bounded barrier wait expired (results invalid)
+ * Weights are rounded to bf16 before the product (the reference's own quantised layer would be
+ * used with float32 weights; tolerance 1e-2 relative as for bf16 activations).
+ */
+int coset_e8_dequant_gemm(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
+                          const void* x_bf16, int64_t ldx, int T, const float* bias, float* y, int64_t ldy,
+                          int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -75,3 +75,21 @@ def test_export_from_trained_layer():
         assert rel(lin(x).cpu().numpy(), layer(x).cpu().numpy()) < 1e-5
     with pytest.raises(ValueError):
         E8CodeLinear.from_weight(torch.zeros(4, 12, device="cuda"), torch.ones(4, device="cuda"), 1)
+
+
+@pytest.mark.parametrize("T,n_out,n_in,tiling", [(128, 128, 64, "block"), (256, 256, 512, "block"), (300, 200, 1024, "row"),
+                                                  (1, 128, 128, "block")])
+def test_tcgen05_dequant_gemm(T, n_out, n_in, tiling):
+    """Fused decode + tensor-core product against decode-then-float32-matmul of the CPU restatement."""
+    from coset_b200.vlut import E8CodeLinear, e8_dequant_gemm
+    W, beta, bpt, digits, w_hat = make(n_out, n_in, tiling, seed=T)
+    bias = torch.randn(n_out)
+    lin = E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt, bias.cuda())
+    x = torch.randn(T, n_in).to(torch.bfloat16)
+    got = e8_dequant_gemm(lin.codes, lin.beta, bpt, x.cuda(), lin.bias, check=True).cpu().numpy()
+    want = x.float().numpy().astype(np.float64) @ w_hat.astype(np.float64).T + bias.double().numpy()
+    assert rel(got, want) < 1e-2
+    # against the same product with bf16-rounded weights the kernel should agree to fp32 accumulation error
+    w_bf = torch.from_numpy(w_hat).to(torch.bfloat16).double().numpy()
+    want_bf = x.double().numpy() @ w_bf.T + bias.double().numpy()
+    assert rel(got, want_bf) < 1e-5
