@@ -97,6 +97,14 @@ def bench_vlut():
             else:
                 rec.update({"bound": "tensor", "TFLOPs": flops / (ms * 1e-3) / 1e12, "frac": flops / (ms * 1e-3) / 1e12 / tf})
             print(json.dumps(rec), flush=True)
+            if T > 64:
+                from .vlut import e8_dequant_gemm
+                e8_dequant_gemm(lin.codes, lin.beta, bpt, x, None, check=True)
+                ms2 = cuda_time(lambda: e8_dequant_gemm(lin.codes, lin.beta, bpt, x, None), iters=20)
+                print(json.dumps({"bench": "vlut_matmul", "tiling": tiling, "T": T, "shape": [n, n], "ms": ms2,
+                                  "tokens_per_s": T / (ms2 * 1e-3), "path": "fused tcgen05 dequant-GEMM (no dense weight in HBM)",
+                                  "bound": "tensor", "TFLOPs": flops / (ms2 * 1e-3) / 1e12,
+                                  "frac": flops / (ms2 * 1e-3) / 1e12 / tf, "peaks": src}), flush=True)
 
 
 def bench_gradcomm():

@@ -1,16 +1,20 @@
 // Large-token code-domain matmul on the 5th-generation tensor cores (tcgen05):
 //     y[T, N] = x[T, K] (bf16) * Wq^T + bias,   Wq = decode(codes) / beta  (never stored in HBM)
 //
-// One CTA owns a 128 (tokens) x 128 (output features) tile of y.  Per 64-wide K step
-//   * the activation tile  A (128 x 64 bf16) is copied to shared memory,
+// One CTA owns a 512 (tokens) x 128 (output features) tile of y: four 128 x 128 accumulators
+// that fill the SM's tensor memory, so that every decoded weight tile is used by four MMAs.
+// Per 64-wide K step
+//   * up to four activation tiles A (128 x 64 bf16 each) are copied to shared memory (cp.async),
 //   * the weight tile      B (128 x 64 bf16) is DECODED into shared memory: one thread turns one
 //     packed E8 code (4 B) plus its scale into eight bf16 weights = one 16-byte chunk,
 // both in the K-major SWIZZLE_128B layout the UMMA shared-memory descriptor describes
-// (8-row groups of 1024 B, 16-byte chunk c of row r stored at chunk c ^ (r & 7)); then one thread
-// issues four tcgen05.mma (M=128, N=128, K=16) that accumulate into tensor memory (128 lanes x
-// 128 fp32 columns) and a tcgen05.commit that releases the stage through an mbarrier.  Three
-// stages let the decode of step k+1.. overlap the MMAs of step k.  The epilogue reads the
-// accumulator with tcgen05.ld and writes fp32.
+// (8-row groups of 1024 B, 16-byte chunk c of row r stored at chunk c ^ (r & 7)).
+// Warp-specialised pipeline over 2 stages: sixteen producer warps fill a stage and arrive on its
+// "full" mbarrier; the first lane of a seventeenth warp waits for "full", issues four tcgen05.mma
+// (M=128, N=128, K=16) per token sub-tile that accumulate into tensor memory and a
+// tcgen05.commit that signals the stage's "empty" mbarrier when those MMAs have retired.  Producer
+// warps therefore run ahead of the tensor core by up to two K steps and are never in lockstep
+// with each other.  The epilogue (producer warps) reads the accumulator with tcgen05.ld.
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel records an error code, still frees
 // its tensor memory and returns.  No cluster features, no multicast, no peer memory.
@@ -24,10 +28,14 @@ using namespace coset;
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64, STAGES = 3, THREADS = 256;
+constexpr int BM = 128, BN = 128, BK = 64, STAGES = 2;
+constexpr int MSUB = 4;                   // token sub-tiles of 128 per CTA: one decoded weight tile feeds 4 MMAs
+constexpr int PRODUCERS = 512;            // 16 warps decode / copy tiles and run the epilogue
+constexpr int THREADS = PRODUCERS + 32;   // + 1 warp whose first lane issues the MMAs
 constexpr int TILE_BYTES = BM * BK * 2;  // 16 KiB, same for A and B
-constexpr uint32_t TMEM_COLS = 128;
-constexpr int SMEM_BYTES = 2 * STAGES * TILE_BYTES + 1024 /*alignment slack*/ + 64 /*barriers, tmem slot*/;
+constexpr uint32_t TMEM_COLS = MSUB * BN;  // 512 fp32 columns = the whole tensor memory of the SM
+constexpr int STAGE_BYTES = (MSUB + 1) * TILE_BYTES;  // MSUB activation tiles + 1 weight tile
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 128 /*barriers, tmem slot*/;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -44,6 +52,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (ok) return true;
     }
     return false;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// 16-byte asynchronous global->shared copy; src_bytes = 0 writes zeros (rows beyond T)
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -90,7 +105,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 1)
 k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ beta, e8::TileDiv td, int N, int K,
                const __nv_bfloat16* __restrict__ x, int64_t ldx, int T, const float* __restrict__ bias,
                const uint2* __restrict__ table, float* __restrict__ y, int64_t ldy, int* __restrict__ status) {
@@ -98,20 +113,27 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;           // tiles need 1024-byte alignment for the 128B swizzle
     uint8_t* gen = smem_raw + (base - raw);                 // generic pointer to the same place
-    const uint32_t a_base = base, b_base = base + STAGES * TILE_BYTES;
-    const uint32_t bar_base = base + 2 * STAGES * TILE_BYTES;  // empty[STAGES], done, then the tmem slot
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + 2 * STAGES * TILE_BYTES + 8 * (STAGES + 1));
+    // stage s: [MSUB activation tiles][weight tile]; barriers: empty[STAGES], full[STAGES], done; tmem slot
+    const uint32_t bar_base = base + STAGES * STAGE_BYTES;
+    const uint32_t full_base = bar_base + 8 * STAGES, done_bar = bar_base + 16 * STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + STAGES * STAGE_BYTES + 16 * STAGES + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile_n = blockIdx.x, tile_m = blockIdx.y;
     const int kb_row = K / 8;  // codes per weight row
+    const int tok0 = tile_m * (MSUB * BM);
+    const int n_sub = (T - tok0 + BM - 1) / BM < MSUB ? (T - tok0 + BM - 1) / BM : MSUB;  // sub-tiles that hold tokens
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (tid == 0) {
-        for (int s = 0; s <= STAGES; ++s) mbar_init(bar_base + 8 * s, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_base + 8 * s, 1);                  // empty: one tcgen05.commit
+            mbar_init(full_base + 8 * s, PRODUCERS / 32);    // full: one arrive per producer warp
+        }
+        mbar_init(done_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -121,70 +143,109 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
     bool ok = true;
 
     const int KT = K / BK;
-    for (int kt = 0; kt < KT; ++kt) {
-        const int s = kt % STAGES;
-        if (kt >= STAGES) ok = mbar_wait(bar_base + 8 * s, (uint32_t)((kt / STAGES - 1) & 1)) && ok;
-        uint8_t* a_gen = gen + s * TILE_BYTES;
-        uint8_t* b_gen = gen + (STAGES + s) * TILE_BYTES;
+    if (warp < PRODUCERS / 32) {
+        // Each producer thread owns 2 (row, chunk) slots of every tile.  Codes and scales of step
+        // kt+1 are loaded into registers before step kt is decoded; activations go global->shared
+        // with cp.async and overlap the table gathers of the decode.
+        constexpr int SLOTS = (BN * 8) / PRODUCERS;
+        uint32_t code_n[SLOTS];
+        float beta_n[SLOTS];
+        auto fetch = [&](int kt) {
 #pragma unroll
-        for (int j = 0; j < (BM * 8) / THREADS; ++j) {  // activations: 128 rows x 8 chunks of 16 B
-            int idx = tid + j * THREADS, row = idx >> 3, c = idx & 7;
-            int tok = tile_m * BM + row;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (tok < T) v = __ldg(reinterpret_cast<const uint4*>(x + (int64_t)tok * ldx + (int64_t)kt * BK + c * 8));
-            *reinterpret_cast<uint4*>(a_gen + swizzled_chunk_offset(row, c)) = v;
-        }
-#pragma unroll
-        for (int j = 0; j < (BN * 8) / THREADS; ++j) {  // weights: one E8 code -> one 16-byte chunk
-            int idx = tid + j * THREADS, row = idx >> 3, c = idx & 7;
-            int n = tile_n * BN + row;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (n < N) {
-                int64_t blk = (int64_t)n * kb_row + (int64_t)kt * 8 + c;
-                uint32_t code = __ldg(codes + blk);
-                float sc = MODE == 2 ? __ldg(beta + e8::tile_of(td, blk)) : 1.0f;
-                float v2[8], w[8];
-                e8::decode_q4m2_twice(code, table, v2);
-                e8::scale_twice<MODE>(v2, sc, w);
-                v = make_uint4(pack_bf16x2(w[0], w[1]), pack_bf16x2(w[2], w[3]), pack_bf16x2(w[4], w[5]), pack_bf16x2(w[6], w[7]));
+            for (int j = 0; j < SLOTS; ++j) {
+                int idx = tid + j * PRODUCERS, row = idx >> 3, c = idx & 7;
+                int n = tile_n * BN + row;
+                code_n[j] = 0u;
+                beta_n[j] = 1.0f;
+                if (n < N) {
+                    int64_t blk = (int64_t)n * kb_row + (int64_t)kt * 8 + c;
+                    code_n[j] = __ldg(codes + blk);
+                    if (MODE == 2) beta_n[j] = __ldg(beta + e8::tile_of(td, blk));
+                }
             }
-            *reinterpret_cast<uint4*>(b_gen + swizzled_chunk_offset(row, c)) = v;
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
-        __syncthreads();
-        if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_addr = a_base + s * TILE_BYTES, b_addr = b_base + s * TILE_BYTES;
+        };
+        fetch(0);
+        for (int kt = 0; kt < KT; ++kt) {
+            const int s = kt % STAGES;
+            uint32_t code_c[SLOTS];
+            float beta_c[SLOTS];
 #pragma unroll
-            for (int k = 0; k < BK / 16; ++k)  // 16 bf16 = 32 bytes along K inside the 128-byte swizzle row
-                umma_f16(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), kIdesc, (kt > 0 || k > 0) ? 1u : 0u);
-            umma_commit(bar_base + 8 * s);                    // stage s may be overwritten once these MMAs retire
-            if (kt == KT - 1) umma_commit(bar_base + 8 * STAGES);  // ... and the accumulator is complete
+            for (int j = 0; j < SLOTS; ++j) { code_c[j] = code_n[j]; beta_c[j] = beta_n[j]; }
+            if (kt + 1 < KT) fetch(kt + 1);
+            if (kt >= STAGES) ok = mbar_wait(bar_base + 8 * s, (uint32_t)((kt / STAGES - 1) & 1)) && ok;
+            const uint32_t stage_addr = base + s * STAGE_BYTES;
+            uint8_t* b_gen = gen + s * STAGE_BYTES + MSUB * TILE_BYTES;
+            for (int a = 0; a < n_sub; ++a) {
+#pragma unroll
+                for (int j = 0; j < SLOTS; ++j) {
+                    int idx = tid + j * PRODUCERS, row = idx >> 3, c = idx & 7;
+                    int tok = tok0 + a * BM + row;
+                    int tok_c = tok < T ? tok : T - 1;  // keep the address valid; 0 source bytes -> zero fill
+                    cp_async16(stage_addr + a * TILE_BYTES + swizzled_chunk_offset(row, c),
+                               x + (int64_t)tok_c * ldx + (int64_t)kt * BK + c * 8, tok < T ? 16u : 0u);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < SLOTS; ++j) {
+                int idx = tid + j * PRODUCERS, row = idx >> 3, c = idx & 7;
+                // weights are rounded to bf16 here, so the scale is applied as one multiply by
+                // 0.5 / beta (relative error 2^-23, far below the bf16 rounding) instead of the
+                // exact IEEE division the float32 paths use; rows beyond N hold code 0 = weight 0
+                float half_inv = MODE == 2 ? __fdividef(0.5f, beta_c[j]) : 0.5f;
+                float v2[8];
+                e8::decode_q4m2_twice(code_c[j], table, v2);
+                uint4 v = make_uint4(pack_bf16x2(v2[0] * half_inv, v2[1] * half_inv), pack_bf16x2(v2[2] * half_inv, v2[3] * half_inv),
+                                     pack_bf16x2(v2[4] * half_inv, v2[5] * half_inv), pack_bf16x2(v2[6] * half_inv, v2[7] * half_inv));
+                *reinterpret_cast<uint4*>(b_gen + swizzled_chunk_offset(row, c)) = v;
+            }
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_base + 8 * s);
+        }
+    } else if (lane == 0) {
+        for (int kt = 0; kt < KT; ++kt) {
+            const int s = kt % STAGES;
+            ok = mbar_wait(full_base + 8 * s, (uint32_t)((kt / STAGES) & 1)) && ok;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t stage_addr = base + s * STAGE_BYTES, b_addr = stage_addr + MSUB * TILE_BYTES;
+            for (int a = 0; a < n_sub; ++a) {
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)  // 16 bf16 = 32 bytes along K inside the 128-byte swizzle row
+                    umma_f16(tmem_d + (uint32_t)(a * BN), umma_desc(stage_addr + a * TILE_BYTES + k * 32), umma_desc(b_addr + k * 32),
+                             kIdesc, (kt > 0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit(bar_base + 8 * s);            // stage s may be overwritten once these MMAs retire
+            if (kt == KT - 1) umma_commit(done_bar);  // ... and the accumulators are complete
         }
     }
-    ok = mbar_wait(bar_base + 8 * STAGES, 0u) && ok;
+    if (!ok && status) atomicExch(status, 1);
+    ok = mbar_wait(done_bar, 0u) && ok;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    // epilogue: warp w reads TMEM lanes 32*(w%4).., columns 64*(w/4)..; thread = one token row
-    {
-        const int q = warp & 3, h = warp >> 2;
-        const int tok = tile_m * BM + q * 32 + lane;
+    // epilogue: producer warp w reads TMEM lanes 32*(w%4).., columns 64*(w/4).. of every accumulator;
+    // one thread = one token row
+    if (warp < PRODUCERS / 32) {
+        const int q = warp & 3, h = (warp >> 2) & 1;
+        for (int a = warp >> 3; a < n_sub; a += PRODUCERS / 256) {
+            const int tok = tok0 + a * BM + q * 32 + lane;
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-            uint32_t r[32];
-            const int col0 = h * 64 + cc * 32;
-            tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, r);
-            if (tok < T && ok) {
-                float* dst = y + (int64_t)tok * ldy + (int64_t)tile_n * BN + col0;
+            for (int cc = 0; cc < 2; ++cc) {
+                uint32_t r[32];
+                const int col0 = h * 64 + cc * 32;
+                tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + col0), r);
+                if (tok < T && ok) {
+                    float* dst = y + (int64_t)tok * ldy + (int64_t)tile_n * BN + col0;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    int n = tile_n * BN + col0 + j;
-                    if (n < N) dst[j] = __uint_as_float(r[j]) + (bias ? __ldg(bias + n) : 0.0f);
+                    for (int j = 0; j < 32; ++j) {
+                        int n = tile_n * BN + col0 + j;
+                        if (n < N) dst[j] = __uint_as_float(r[j]) + (bias ? __ldg(bias + n) : 0.0f);
+                    }
                 }
             }
         }
     }
-    if (!ok && tid == 0 && status) atomicExch(status, 1);
+    if (!ok && status) atomicExch(status, 1);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
@@ -207,7 +268,7 @@ extern "C" int coset_e8_dequant_gemm(const void* codes, const float* beta, int64
     const uint2* table = residual_table_q4(st);
     if (!table) return COSET_E_STATE;
     e8::TileDiv td = e8::make_tile_div(beta ? blocks_per_tile : 1, (int64_t)n_out * (n_in / 8));
-    dim3 grid((n_out + BN - 1) / BN, (T + BM - 1) / BM);
+    dim3 grid((n_out + BN - 1) / BN, (T + MSUB * BM - 1) / (MSUB * BM));
     if (grid.y > 65535) return fail(COSET_E_UNSUPPORTED, "T too large");
     if (beta) {
         if (int e = check_cuda(cudaFuncSetAttribute(k_dequant_gemm<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), "cudaFuncSetAttribute")) return e;
