@@ -55,6 +55,7 @@ k_vlut_gemv(const uint32_t* __restrict__ codes, const float* __restrict__ beta, 
 #pragma unroll
     for (int t = 0; t < TT; ++t) acc[t] = 0.0f;
     const int64_t row_base = (int64_t)row * kb;
+#pragma unroll 4
     for (int blk = lane; blk < kb; blk += 32) {
         uint32_t code = __ldcs(codes + row_base + blk);
         float s = 1.0f;
