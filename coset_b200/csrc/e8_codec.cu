@@ -216,12 +216,28 @@ k_encode_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::T
 constexpr int kQueueSlots = 64;   // < 32 left after a drain + at most 32 new per step
 constexpr int kEncWarps = kThreads / 32;
 
-template <int DT, int MODE>
+// RECON = false: codes only (e8_encode).  RECON = true: the fused round trip -- every finished code is
+// decoded through the residual table, unscaled, clamped and written as [n, 8] of type DTO; the
+// packed code is stored only if `codes` is not null (e8_quantize / the layer's weight path).
+template <int DT, int MODE, bool RECON, int DTO>
 __global__ void __launch_bounds__(kThreads, 4)
 k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
-                     uint32_t* __restrict__ codes) {
+                     uint32_t* __restrict__ codes, const uint2* __restrict__ table, void* __restrict__ out, float clip) {
     __shared__ float q_x[kEncWarps][8][kQueueSlots];
-    __shared__ uint32_t q_meta[kEncWarps][4][kQueueSlots];  // code so far, block index lo / hi, first open level
+    __shared__ uint32_t q_meta[kEncWarps][5][kQueueSlots];  // code so far, block index lo / hi, first open level, scale
+    auto emit = [&](int64_t b, uint32_t code, float s) {
+        if (!RECON) {
+            __stcs(codes + b, code);
+        } else {
+            if (codes) __stcs(codes + b, code);
+            float v2[8], xh[8];
+            e8::decode_q4m2_twice(code, table, v2);
+            e8::scale_twice<MODE>(v2, s, xh);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) xh[i] = clampf(xh[i], clip);
+            e8::Row8<DTO>::store(out, b, xh);
+        }
+    };
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t lanes_below = (1u << lane) - 1u;
     int count = 0;  // warp-uniform number of queued blocks
@@ -271,7 +287,7 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
             }
             const bool defer = active && open_level != 2;
             const uint32_t bal = __ballot_sync(0xffffffffu, defer);
-            if (active && !defer) __stcs(codes + b, code);
+            if (active && !defer) emit(b, code, s);
             if (defer) {
                 const int pos = count + __popc(bal & lanes_below);
 #pragma unroll
@@ -280,6 +296,7 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
                 q_meta[warp][1][pos] = (uint32_t)b;
                 q_meta[warp][2][pos] = (uint32_t)((uint64_t)b >> 32);
                 q_meta[warp][3][pos] = (uint32_t)open_level;
+                q_meta[warp][4][pos] = __float_as_uint(s);
             }
             count += __popc(bal);
             base += stride;
@@ -295,21 +312,22 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
                 uint32_t code = q_meta[warp][0][lane];
                 int64_t b = (int64_t)(((uint64_t)q_meta[warp][2][lane] << 32) | q_meta[warp][1][lane]);
                 int start = (int)q_meta[warp][3][lane];
-                __stcs(codes + b, e8::finish_block_q4(v, code, start));
+                float sc = __uint_as_float(q_meta[warp][4][lane]);
+                emit(b, e8::finish_block_q4(v, code, start), sc);
             }
             __syncwarp();
             const int rem = count - take;
             if (lane < rem) {  // move the tail (fewer than 32 entries) to the front
                 float t[8];
-                uint32_t u[4];
+                uint32_t u[5];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) t[i] = q_x[warp][i][32 + lane];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) u[i] = q_meta[warp][i][32 + lane];
+                for (int i = 0; i < 5; ++i) u[i] = q_meta[warp][i][32 + lane];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) q_x[warp][i][lane] = t[i];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) q_meta[warp][i][lane] = u[i];
+                for (int i = 0; i < 5; ++i) q_meta[warp][i][lane] = u[i];
             }
             __syncwarp();
             count = rem;
@@ -344,27 +362,6 @@ k_decode_q4m2(const uint32_t* __restrict__ codes, const float* __restrict__ scal
             e8::Row8<DT>::store(out, b, xh);
         }
     }
-}
-
-template <int DTI, int DTO, int MODE>
-__global__ void __launch_bounds__(kThreads)
-k_quantize_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n, float clip,
-                const uint2* __restrict__ table, void* __restrict__ out, uint32_t* __restrict__ codes) {
-    int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    if (b >= n) return;
-    float v[8];
-    e8::Row8<DTI>::load(x, b, v);
-    float s = load_scale<MODE>(scale, td, b);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = scale_in<MODE>(v[i], s);
-    uint32_t code = e8::encode_q4m2<false>(v);
-    if (codes) codes[b] = code;
-    float v2[8], xh[8];
-    e8::decode_q4m2_twice(code, table, v2);
-    e8::scale_twice<MODE>(v2, s, xh);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) xh[i] = clampf(xh[i], clip);
-    e8::Row8<DTO>::store(out, b, xh);
 }
 
 // Residual table of the q=4 decoder, produced by the literal float32 decoder itself:
@@ -499,7 +496,7 @@ int coset_e8_encode(const void* x, int x_dtype, const float* scale, int scale_mo
     if (q == 4 && M == 2 && sem == COSET_SEM_CORE) {
         // persistent warps: 16 CTAs per SM worth of grid (4 resident at a time) balances queue fill and tail
         unsigned qgrid = grid < (unsigned)(sm_count() * 16) ? grid : (unsigned)(sm_count() * 16);
-        DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2_queued<DT, MODE><<<qgrid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes))))
+        DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2_queued<DT, MODE, false, 0><<<qgrid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes, nullptr, nullptr, 0.0f))))
     } else if (q == 4 && M == 2) {
         DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2<DT, MODE, true><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes))))
     } else if (q <= 4) {
@@ -548,7 +545,8 @@ int coset_e8_quantize(const void* x, int x_dtype, const float* scale, int scale_
     if (q == 4 && M == 2) {
         const uint2* table = residual_table_q4(st);
         if (!table) return COSET_E_STATE;
-        DISPATCH_DT(x_dtype, DTI, DISPATCH_DT(out_dtype, DTO, DISPATCH_MODE(scale_mode, (k_quantize_q4m2<DTI, DTO, MODE><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, clip, table, out, (uint32_t*)codes_out)))))
+        unsigned qgrid = grid < (unsigned)(sm_count() * 16) ? grid : (unsigned)(sm_count() * 16);
+        DISPATCH_DT(x_dtype, DTI, DISPATCH_DT(out_dtype, DTO, DISPATCH_MODE(scale_mode, (k_encode_q4m2_queued<DTI, MODE, true, DTO><<<qgrid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes_out, table, out, clip)))))
     } else if (q <= 4) {
         DISPATCH_DT(x_dtype, DTI, DISPATCH_DT(out_dtype, DTO, DISPATCH_MODE(scale_mode, (k_quantize_generic<DTI, DTO, MODE, 2><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, q, M, clip, out, codes_out)))))
     } else {
