@@ -136,6 +136,46 @@ def bench_vlut():
                                   "frac": flops / (ms2 * 1e-3) / 1e12 / tf, "peaks": src}), flush=True)
 
 
+def bench_vlut_sharded():
+    """Config-4 weight split along the output features over the ranks of a torchrun launch: every
+    rank multiplies its [4096 / W, 4096] slice, one all-gather of the outputs follows."""
+    import torch.distributed as dist
+    from .vlut import ColumnParallelE8CodeLinear
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.manual_seed(0)
+    n = 4096
+    W = (torch.randn(n, n) * 0.02).cuda()
+    beta = torch.full((n * n // 8,), 25.0, device="cuda")
+    lin = ColumnParallelE8CodeLinear.from_weight(W, beta, 1, small_t_max=64)
+    for T in (1, 16, 256, 4096):
+        x = torch.randn(T, n, device="cuda").to(torch.bfloat16)
+        res = {}
+        for name, fn in (("sharded_ms", lambda: lin(x)), ("local_product_ms", lambda: lin.local(x))):
+            for _ in range(5):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(20):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b) / 20], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res[name] = float(t.item())
+        if rank == 0:
+            res.update({"bench": "vlut_matmul_column_parallel", "n_gpus": world, "T": T, "shape": [n, n],
+                        "tokens_per_s": T / (res["sharded_ms"] * 1e-3), "gathered_bytes_per_rank": T * n // world * 4,
+                        "timing": "CUDA events over eager calls, max over ranks"})
+            print(json.dumps(res), flush=True)
+    dist.destroy_process_group()
+
+
 def bench_gradcomm():
     import torch.distributed as dist
     from .gradcomm import E8GradientExchange, bert_base_gradient_numel
@@ -200,6 +240,8 @@ def main(argv=None):
         bench_qat()
     if which in ("vlut", "all"):
         bench_vlut()
+    if which == "vlut_sharded":
+        bench_vlut_sharded()
     if which in ("gradcomm", "all"):
         bench_gradcomm()
 

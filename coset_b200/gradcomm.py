@@ -95,7 +95,7 @@ class E8GradientExchange:
         return res
 
 
-def e8_allreduce_hook(state: E8GradientExchange, bucket) -> torch.futures.Future:
+def e8_allreduce_hook(state: E8GradientExchange, bucket) -> torch.futures.Future[torch.Tensor]:
     """torch DDP communication hook: `ddp.register_comm_hook(E8GradientExchange(group), e8_allreduce_hook)`.
 
     The bucket's flat gradient is replaced by its E8-quantised average."""

@@ -140,3 +140,64 @@ class E8CodeLinear(nn.Module):
                 b = self.bias.to(x2.dtype) if self.bias is not None else None
                 y = torch.nn.functional.linear(x2, self._dense.to(x2.dtype), b)
         return y.reshape(*lead, self.out_features)
+
+
+def out_feature_shard(n_out: int, world: int, rank: int):
+    """[start, stop) of the output features rank `rank` owns: contiguous, equal sizes (n_out must
+    divide by world so that the gathered result needs no padding)."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world of {world}")
+    if n_out % world:
+        raise ValueError(f"out_features {n_out} must be divisible by the world size {world}")
+    per = n_out // world
+    return rank * per, (rank + 1) * per
+
+
+def assemble_gathered(gathered: torch.Tensor) -> torch.Tensor:
+    """[world, T, n_out / world] (the layout an all-gather of the local products yields) -> [T, n_out]."""
+    world, T, per = gathered.shape
+    return gathered.permute(1, 0, 2).reshape(T, world * per)
+
+
+class ColumnParallelE8CodeLinear(nn.Module):
+    """E8CodeLinear sharded along the output features over a process group: every rank owns the
+    codes and scales of out_features / world rows, multiplies the (replicated) activations with
+    them and the slices are exchanged with one all-gather of [T, out_features / world] floats.
+
+    The codes never cross the link; at T = 1 the all-gather is latency-bound."""
+
+    def __init__(self, local: E8CodeLinear, out_features: int, group=None):
+        super().__init__()
+        import torch.distributed as dist
+        self.local = local
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.out_features = out_features
+        self.in_features = local.in_features
+        lo, hi = out_feature_shard(out_features, self.world, self.rank)
+        if local.out_features != hi - lo:
+            raise ValueError(f"local shard has {local.out_features} rows, expected {hi - lo}")
+
+    @classmethod
+    def from_weight(cls, weight: torch.Tensor, beta: torch.Tensor, blocks_per_tile: int, bias=None, group=None, **kw):
+        """Quantise this rank's rows of a full [n_out, n_in] weight; beta holds the scales of the
+        full weight (one per block for blocks_per_tile = 1, one per row for n_in / 8)."""
+        import torch.distributed as dist
+        n_out, n_in = weight.shape
+        lo, hi = out_feature_shard(n_out, dist.get_world_size(group), dist.get_rank(group))
+        tiles_per_row = (n_in // 8) // int(blocks_per_tile)
+        if tiles_per_row * int(blocks_per_tile) * 8 != n_in:
+            raise ValueError("a scale tile must not straddle two rows")
+        b = beta.contiguous().view(-1)[lo * tiles_per_row:hi * tiles_per_row]
+        local = E8CodeLinear.from_weight(weight[lo:hi].contiguous(), b, blocks_per_tile,
+                                         bias[lo:hi] if bias is not None else None, **kw)
+        return cls(local, n_out, group)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+        lead = x.shape[:-1]
+        y_loc = self.local(x.reshape(-1, self.in_features)).contiguous()
+        gathered = torch.empty(self.world * y_loc.numel(), dtype=y_loc.dtype, device=y_loc.device)
+        dist.all_gather_into_tensor(gathered, y_loc.view(-1), group=self.group)
+        return assemble_gathered(gathered.view(self.world, *y_loc.shape)).reshape(*lead, self.out_features)

@@ -84,3 +84,57 @@ def test_two_gpu_nccl_exchange(tmp_path):
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stderr[-2000:]
     assert "EXCHANGE_OK" in res.stdout
+
+
+DDP_WORKER = r'''
+import os, sys
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+sys.path.insert(0, sys.argv[1])
+from coset_b200.gradcomm import E8GradientExchange, e8_allreduce_hook
+rank = int(os.environ["RANK"]); local = int(os.environ["LOCAL_RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(local)
+dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+torch.manual_seed(0)
+model = nn.Sequential(nn.Linear(64, 48), nn.Tanh(), nn.Linear(48, 10)).cuda()
+ddp = nn.parallel.DistributedDataParallel(model, device_ids=[local])
+ex = E8GradientExchange(scale=500.0)
+ddp.register_comm_hook(ex, e8_allreduce_hook)
+g = torch.Generator().manual_seed(100 + rank)
+x = torch.randn(32, 64, generator=g).cuda()
+loss = ddp(x).square().mean() * 0.01  # keeps every gradient inside the two-level code range at scale 500
+loss.backward()
+torch.cuda.synchronize()
+flat = torch.cat([p.grad.reshape(-1) for p in model.parameters()])
+# every rank must hold the same bits
+gathered = [torch.empty_like(flat) for _ in range(world)]
+dist.all_gather(gathered, flat)
+assert all(torch.equal(gathered[0], t) for t in gathered), "ranks disagree after the hook"
+# and they must be close to the exact mean of the local gradients (quantisation step 0.5 / 500 per value)
+plain = nn.Sequential(nn.Linear(64, 48), nn.Tanh(), nn.Linear(48, 10)).cuda()
+plain.load_state_dict(model.state_dict())
+(plain(x).square().mean() * 0.01).backward()
+exact = torch.cat([p.grad.reshape(-1) for p in plain.parameters()])
+dist.all_reduce(exact)
+exact /= world
+err = (flat - exact).abs()
+assert float(exact.abs().max()) < 4.0 / 500.0, float(exact.abs().max())
+assert float(err.max()) <= 1.5 / 500.0 + 1e-7, float(err.max())
+if rank == 0:
+    print("DDP_HOOK_OK")
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_ddp_comm_hook(tmp_path):
+    script = tmp_path / "ddp_worker.py"
+    script.write_text(DDP_WORKER)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29619", str(script), ROOT]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert "DDP_HOOK_OK" in res.stdout

@@ -1,5 +1,7 @@
 """Code-domain matmul (E8CodeLinear) against decode-then-float32-matmul of the CPU restatement
 of the reference (BASELINE config: weight stored as E8 codes, activations bf16 / float32)."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -93,3 +95,45 @@ def test_tcgen05_dequant_gemm(T, n_out, n_in, tiling):
     w_bf = torch.from_numpy(w_hat).to(torch.bfloat16).double().numpy()
     want_bf = x.double().numpy() @ w_bf.T + bias.double().numpy()
     assert rel(got, want_bf) < 2e-3  # weights may differ from the exactly divided ones by one bf16 ulp
+
+
+SHARD_WORKER = r'''
+import os, sys
+import torch
+import torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from coset_b200.vlut import ColumnParallelE8CodeLinear, E8CodeLinear
+rank = int(os.environ["RANK"]); local = int(os.environ["LOCAL_RANK"])
+torch.cuda.set_device(local)
+dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+torch.manual_seed(3)
+n_out, n_in = 256, 512
+W = (torch.randn(n_out, n_in) * 0.02).cuda()
+for bpt, nbeta in ((1, n_out * n_in // 8), (n_in // 8, n_out)):
+    beta = (20.0 + 10.0 * torch.rand(nbeta)).cuda()
+    bias = torch.randn(n_out).cuda()
+    full = E8CodeLinear.from_weight(W, beta, bpt, bias)
+    shard = ColumnParallelE8CodeLinear.from_weight(W, beta, bpt, bias)
+    for T in (1, 5, 200):
+        x = torch.randn(T, n_in).cuda()
+        assert torch.equal(shard(x), full(x)), (bpt, T)
+torch.cuda.synchronize()
+if rank == 0:
+    print("SHARD_OK")
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_column_parallel_equals_unsharded(tmp_path):
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "shard_worker.py"
+    script.write_text(SHARD_WORKER)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29621", str(script), root]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert "SHARD_OK" in res.stdout

@@ -64,3 +64,42 @@ def test_single_process_without_process_group():
     avg = E8GradientExchange(scale=500.0, codec=OracleCodec()).all_reduce_mean(grad)
     assert avg.shape == grad.shape
     assert float((avg - grad).abs().median()) < 0.5 / 500.0
+
+
+def _ddp_worker(rank, world, port, out_dir):
+    sys.path.insert(0, os.path.dirname(HERE))
+    sys.path.insert(0, HERE)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import torch.nn as nn
+    from coset_b200.gradcomm import E8GradientExchange, e8_allreduce_hook
+    from gradcomm_util import OracleCodec
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(16, 12), nn.Tanh(), nn.Linear(12, 3))
+    ddp = nn.parallel.DistributedDataParallel(model)
+    ddp.register_comm_hook(E8GradientExchange(scale=500.0, codec=OracleCodec()), e8_allreduce_hook)
+    g = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(8, 16, generator=g)
+    (ddp(x).square().mean() * 0.01).backward()
+    flat = torch.cat([p.grad.reshape(-1) for p in model.parameters()])
+    plain = nn.Sequential(nn.Linear(16, 12), nn.Tanh(), nn.Linear(12, 3))
+    plain.load_state_dict(model.state_dict())
+    (plain(x).square().mean() * 0.01).backward()
+    exact = torch.cat([p.grad.reshape(-1) for p in plain.parameters()])
+    dist.all_reduce(exact)
+    exact /= world
+    np.save(os.path.join(out_dir, f"ddp{rank}.npy"), np.stack([flat.numpy(), exact.numpy()]))
+    dist.destroy_process_group()
+
+
+def test_ddp_comm_hook_on_cpu_ranks(tmp_path):
+    """The hook registered on a real DistributedDataParallel module (gloo): DDP accepts its
+    signature, every rank ends with the same gradient, close to the exact mean."""
+    port = 33500 + (os.getpid() % 2000)
+    mp.spawn(_ddp_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    got = [np.load(tmp_path / f"ddp{r}.npy") for r in range(2)]
+    assert np.array_equal(got[0][0], got[1][0])
+    err = np.abs(got[0][0] - got[0][1])
+    assert err.max() <= 1.5 / 500.0 + 1e-7, err.max()
+    assert np.abs(got[0][1]).max() < 4.0 / 500.0  # the gradients stay inside the code range
