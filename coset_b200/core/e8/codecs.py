@@ -76,14 +76,25 @@ def e8_encode_packed(x: torch.Tensor, q: int = 4, M: int = 2, scale=None, scale_
 
 def e8_decode_packed(codes: torch.Tensor, q: int = 4, M: int = 2, scale=None, scale_mode: int = _lib.SCALE_NONE,
                      blocks_per_tile: int = 1, dtype: torch.dtype = torch.float32,
-                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """packed codes (as produced by e8_encode_packed) -> reconstruction [N, 8]."""
+                     out: Optional[torch.Tensor] = None, depth: Optional[int] = None) -> torch.Tensor:
+    """packed codes (as produced by e8_encode_packed) -> reconstruction [N, 8].
+
+    depth (1 .. M): coarse-to-fine reconstruction from the `depth` coarsest levels only, the
+    float32 counterpart of ref/hnlq.py:447-507.  The residual of an all-zero level word is the
+    zero vector, so the finer level words are cleared and the full decoder runs."""
     _lib.require_cuda(codes, "codes")
     nbytes = _code_dtype(q, M)
     total = codes.numel() * codes.element_size()
     if total % nbytes or not codes.is_contiguous():
         raise ValueError("codes is not a contiguous array of packed block codes")
     n = total // nbytes
+    if depth is not None:
+        if not (1 <= depth <= M):
+            raise ValueError(f"depth must be between 1 and {M}, got {depth}")
+        if depth < M:
+            levels = codes.view(torch.uint8).reshape(n, M, nbytes // M).clone()
+            levels[:, :M - depth] = 0
+            codes = levels.view(-1)
     scale_t, mode, bpt = _scale_args(scale, scale_mode, n, blocks_per_tile, codes.device)
     if out is None:
         out = torch.empty((n, 8), dtype=dtype, device=codes.device)

@@ -126,13 +126,18 @@ __global__ void __launch_bounds__(kThreads) k_ref_encode(const double* __restric
 }
 
 __global__ void __launch_bounds__(kThreads) k_ref_decode(const int32_t* __restrict__ digits, const int32_t* __restrict__ T,
-                                                         int64_t n, RefParams p, double* __restrict__ out) {
+                                                         int64_t n, RefParams p, int first_level,
+                                                         double* __restrict__ out) {
     int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (b >= n) return;
     double acc[8], w = 1.0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.0;
     for (int m = 0; m < p.M; ++m) {
+        if (m < first_level) {  // coarse-to-fine: the finest levels are left out, their weight still advances
+            w = __dmul_rn(w, (double)p.q);
+            continue;
+        }
         const int32_t* d = digits + (b * p.M + m) * 8;
         double gb[8], s[8], pr[8];
         double hb = __dmul_rn(0.5, (double)d[7]);
@@ -178,15 +183,21 @@ int coset_e8_ref_encode(const double* x, int64_t n_blocks, double beta, double a
     return check_launch("e8_ref_encode");
 }
 
-int coset_e8_ref_decode(const int32_t* digits, const int32_t* T, int64_t n_blocks, double beta, double alpha, int q, int M,
-                        const double* dither_host, double* out, void* stream) {
+int coset_e8_ref_decode_coarse(const int32_t* digits, const int32_t* T, int64_t n_blocks, double beta, double alpha, int q,
+                               int M, int depth, const double* dither_host, double* out, void* stream) {
     RefParams p;
     if (int e = fill(p, beta, alpha, q, M, 0, 0, dither_host)) return e;
+    if (depth < 1 || depth > M) return fail(COSET_E_BADARG, "depth must be between 1 and M");
     if (n_blocks < 0) return fail(COSET_E_BADARG, "n_blocks is negative");
     if (n_blocks == 0) return 0;
     if (!digits || !T || !out) return fail(COSET_E_BADARG, "null pointer");
-    k_ref_decode<<<(unsigned)((n_blocks + kThreads - 1) / kThreads), kThreads, 0, (cudaStream_t)stream>>>(digits, T, n_blocks, p, out);
+    k_ref_decode<<<(unsigned)((n_blocks + kThreads - 1) / kThreads), kThreads, 0, (cudaStream_t)stream>>>(digits, T, n_blocks, p, M - depth, out);
     return check_launch("e8_ref_decode");
+}
+
+int coset_e8_ref_decode(const int32_t* digits, const int32_t* T, int64_t n_blocks, double beta, double alpha, int q, int M,
+                        const double* dither_host, double* out, void* stream) {
+    return coset_e8_ref_decode_coarse(digits, T, n_blocks, beta, alpha, q, M, M, dither_host, out, stream);
 }
 
 }  // extern "C"

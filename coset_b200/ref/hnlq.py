@@ -6,7 +6,7 @@ T `[N]` int32).  Results are bit-identical to ref.hnlq.HNLQ run vector by vector
 """
 import ctypes
 from dataclasses import dataclass
-from typing import Tuple
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -92,8 +92,7 @@ class HNLQ:
             return tuple(digits[0, m].cpu().numpy().astype(int) for m in range(c.M)), int(T[0])
         return digits, T
 
-    def decode(self, b_list, T, with_dither: bool = False):
-        """HNLQ.decode (ref/hnlq.py:422-445)."""
+    def _decode_levels(self, b_list, T, depth):
         c = self.config
         single = not isinstance(b_list, torch.Tensor)
         if single:
@@ -107,10 +106,48 @@ class HNLQ:
         n = digits.shape[0]
         out = torch.empty((n, 8), dtype=torch.float64, device=self.device)
         with torch.cuda.device(self.device):
-            rc = _lib.lib().coset_e8_ref_decode(_lib.ptr(digits), _lib.ptr(Tt), n, c.beta, c.alpha, c.q, c.M,
-                                                ctypes.cast(self._dither, ctypes.c_void_p), _lib.ptr(out), _lib.stream())
-        _lib.check(rc, "coset_e8_ref_decode")
+            rc = _lib.lib().coset_e8_ref_decode_coarse(_lib.ptr(digits), _lib.ptr(Tt), n, c.beta, c.alpha, c.q, c.M,
+                                                       int(depth), ctypes.cast(self._dither, ctypes.c_void_p),
+                                                       _lib.ptr(out), _lib.stream())
+        _lib.check(rc, "coset_e8_ref_decode_coarse")
         return out[0].cpu().numpy() if single else out
+
+    def decode(self, b_list, T, with_dither: bool = False):
+        """HNLQ.decode (ref/hnlq.py:422-445)."""
+        if with_dither:
+            raise NotImplementedError("subtractive dither is all-zero in the reference unless set by hand")
+        return self._decode_levels(b_list, T, self.config.M)
+
+    def decode_coarse_to_fine(self, b_list, T, with_dither: bool = False, depth: Optional[int] = None):
+        """HNLQ.decode_coarse_to_fine (ref/hnlq.py:447-507): the `depth` coarsest levels only."""
+        if with_dither:
+            raise NotImplementedError("subtractive dither is all-zero in the reference unless set by hand")
+        if depth is None:
+            return self.decode(b_list, T, with_dither)
+        if not (1 <= depth <= self.config.M):
+            raise ValueError(f"depth must be between 1 and {self.config.M}, got {depth}")
+        return self._decode_levels(b_list, T, depth)
+
+    def decode_progressive(self, b_list, T, with_dither: bool = False) -> List:
+        """HNLQ.decode_progressive (ref/hnlq.py:509-536): reconstructions for depth 1 .. M."""
+        return [self.decode_coarse_to_fine(b_list, T, with_dither, level) for level in range(1, self.config.M + 1)]
+
+    def get_default_decoding(self, b_list, T, with_dither: bool = False, depth: Optional[int] = None):
+        """HNLQ.get_default_decoding (ref/hnlq.py:538-571): dispatch on config.decoding."""
+        d = self.config.decoding
+        if d == "full":
+            return self.decode(b_list, T, with_dither)
+        if d == "coarse_to_fine":
+            return self.decode_coarse_to_fine(b_list, T, with_dither, depth=depth)
+        if d == "progressive":
+            return self.decode_progressive(b_list, T, with_dither)
+        raise ValueError(f"Unknown decoding method: {d}")
+
+    def decode_with_depth(self, b_list, T, depth: int, with_dither: bool = False):
+        """HNLQ.decode_with_depth (ref/hnlq.py:573-601)."""
+        if depth < 1 or depth > self.config.M:
+            raise ValueError(f"Depth must be between 1 and {self.config.M}, got {depth}")
+        return self.decode_coarse_to_fine(b_list, T, with_dither, depth)
 
     def quantize(self, x, with_dither: bool = False):
         """encode followed by decode (ref/hnlq.py:608-628)."""

@@ -224,6 +224,14 @@ int coset_e8_ref_encode(const double* x, int64_t n_blocks, double beta, double a
 int coset_e8_ref_decode(const int32_t* digits, const int32_t* T, int64_t n_blocks, double beta,
                         double alpha, int q, int M, const double* dither_host, double* out,
                         void* stream);
+/*
+ * HNLQ.decode_coarse_to_fine (ref/hnlq.py:447-507): reconstruction from the `depth` coarsest
+ * levels only (levels M-depth .. M-1), 1 <= depth <= M; depth == M equals coset_e8_ref_decode.
+ * HNLQ.decode_progressive (ref/hnlq.py:509-536) is this call for depth = 1 .. M.
+ */
+int coset_e8_ref_decode_coarse(const int32_t* digits, const int32_t* T, int64_t n_blocks,
+                               double beta, double alpha, int q, int M, int depth,
+                               const double* dither_host, double* out, void* stream);
 
 /*
  * Code-domain product for MANY tokens on the tcgen05 tensor cores: same result as

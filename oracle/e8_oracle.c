@@ -411,24 +411,35 @@ void e8o_ref_encode(const double* x, int64_t n, double beta, double alpha, int q
     }
 }
 
-/* HNLQ.decode (ref/hnlq.py:389-445). out: [n][8] float64. */
-void e8o_ref_decode(const int32_t* digits, const int32_t* T, int64_t n, double beta, double alpha, int q, int M,
-                    const double* dither, double* out) {
+/* HNLQ.decode_coarse_to_fine (ref/hnlq.py:447-507): the `depth` coarsest levels only, i.e. levels
+ * M-depth .. M-1; depth == M is HNLQ.decode (ref/hnlq.py:389-445).  Every term is an exact multiple
+ * of 1/2 far below 2^53, so the reference's summation order (coarsest first) and this one agree.
+ * out: [n][8] float64. */
+void e8o_ref_decode_depth(const int32_t* digits, const int32_t* T, int64_t n, double beta, double alpha, int q, int M,
+                          int depth, const double* dither, double* out) {
     for (int64_t b = 0; b < n; ++b) {
         double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, w = 1.0;
         for (int m = 0; m < M; ++m) {
-            double gb[8], s[8], pr[8];
-            for (int j = 0; j < 8; ++j) {
-                double a = 0.0;
-                for (int i = 0; i < 8; ++i) a += (double)G[j][i] * (double)digits[(b * M + m) * 8 + i];
-                gb[j] = a;
-                s[j] = a / (double)q;
+            if (m >= M - depth) {
+                double gb[8], s[8], pr[8];
+                for (int j = 0; j < 8; ++j) {
+                    double a = 0.0;
+                    for (int i = 0; i < 8; ++i) a += (double)G[j][i] * (double)digits[(b * M + m) * 8 + i];
+                    gb[j] = a;
+                    s[j] = a / (double)q;
+                }
+                r_qnn(s, dither, pr);
+                for (int j = 0; j < 8; ++j) acc[j] = acc[j] + w * (gb[j] - (double)q * pr[j]);
             }
-            r_qnn(s, dither, pr);
-            for (int j = 0; j < 8; ++j) acc[j] = acc[j] + w * (gb[j] - (double)q * pr[j]);
             w *= (double)q;
         }
         double up = pow(2.0, alpha * (double)T[b]);
         for (int j = 0; j < 8; ++j) out[b * 8 + j] = (beta * acc[j]) * up;
     }
+}
+
+/* HNLQ.decode (ref/hnlq.py:389-445). out: [n][8] float64. */
+void e8o_ref_decode(const int32_t* digits, const int32_t* T, int64_t n, double beta, double alpha, int q, int M,
+                    const double* dither, double* out) {
+    e8o_ref_decode_depth(digits, T, n, beta, alpha, q, M, M, dither, out);
 }

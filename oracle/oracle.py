@@ -170,12 +170,14 @@ def ref_encode(x, beta=1.0, alpha=1.0, q=4, M=2, overload=True, max_iter=10, dit
     return digits, T
 
 
-def ref_decode(digits, T, beta=1.0, alpha=1.0, q=4, dither=None):
+def ref_decode(digits, T, beta=1.0, alpha=1.0, q=4, dither=None, depth=None):
+    """ref.hnlq.HNLQ.decode, or decode_coarse_to_fine(depth) when depth is given."""
     digits = np.ascontiguousarray(digits, dtype=np.int32)
     T = np.ascontiguousarray(T, dtype=np.int32)
     n, M, _ = digits.shape
     d = np.ascontiguousarray(TIE_DITHER if dither is None else dither, dtype=np.float64)
     out = np.empty((n, 8), np.float64)
-    lib().e8o_ref_decode(digits.ctypes.data_as(_i32p), T.ctypes.data_as(_i32p), ctypes.c_int64(n), ctypes.c_double(beta),
-                         ctypes.c_double(alpha), q, M, d.ctypes.data_as(_f64p), out.ctypes.data_as(_f64p))
+    lib().e8o_ref_decode_depth(digits.ctypes.data_as(_i32p), T.ctypes.data_as(_i32p), ctypes.c_int64(n),
+                               ctypes.c_double(beta), ctypes.c_double(alpha), q, M, M if depth is None else int(depth),
+                               d.ctypes.data_as(_f64p), out.ctypes.data_as(_f64p))
     return out

@@ -34,3 +34,24 @@ for tag, beta, over, q, M, alpha in cases:
     print(tag, "T>0:", (T > 0).mean(), "max digit", digits.max())
 np.savez_compressed(os.path.join(OUT, "ref_mode.npz"), **out)
 print(os.path.getsize(os.path.join(OUT, "ref_mode.npz")))
+
+# decode_coarse_to_fine / decode_progressive (ref/hnlq.py:447-536) on the codes above
+coarse = {}
+n_c = 400
+for tag, beta, over, q, M, alpha in cases:
+    if tag not in ("b025", "q3m3", "b01"):
+        continue
+    h = HNLQ.create_e8_quantizer(q=q, M=M, beta=beta, alpha=alpha, overload=over)
+    digits, T = out[f"{tag}_digits"], out[f"{tag}_T"]
+    res = np.empty((M, n_c, 8))
+    for i in range(n_c):
+        b_list = tuple(digits[i, m] for m in range(M))
+        prog = h.decode_progressive(b_list, int(T[i]))
+        for depth in range(1, M + 1):
+            one = h.decode_coarse_to_fine(b_list, int(T[i]), depth=depth)
+            assert np.array_equal(one, prog[depth - 1])
+            res[depth - 1, i] = one
+        assert np.array_equal(res[M - 1, i], out[f"{tag}_xhat"][i])
+    coarse[f"{tag}_by_depth"] = res
+np.savez_compressed(os.path.join(OUT, "ref_coarse.npz"), **coarse)
+print(os.path.getsize(os.path.join(OUT, "ref_coarse.npz")))

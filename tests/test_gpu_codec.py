@@ -169,6 +169,25 @@ def test_per_tile_scales_vs_oracle(e8):
         assert np.array_equal(bits(xh.cpu().numpy()), bits(want_xh))
 
 
+@pytest.mark.parametrize("q,M", [(4, 2), (3, 3), (8, 2)])
+def test_coarse_to_fine_packed_decode(e8, q, M):
+    """depth = d keeps the d coarsest levels: equal to decoding digits whose finer levels are zero."""
+    rng = np.random.default_rng(8)
+    x = (rng.standard_normal((5000, 8)) * (q ** M) / 8).astype(np.float32)
+    digits = O.encode(x, q=q, M=M)
+    codes = e8.e8_encode_packed(dev(x), q, M)
+    for depth in range(1, M + 1):
+        kept = digits.copy()
+        kept[:, :M - depth] = 0
+        want = O.decode(kept, q=q)
+        got = e8.e8_decode_packed(codes, q, M, depth=depth).cpu().numpy()
+        assert np.array_equal(bits(got), bits(want)), depth
+    assert np.array_equal(bits(e8.e8_decode_packed(codes, q, M, depth=M).cpu().numpy()),
+                          bits(e8.e8_decode_packed(codes, q, M).cpu().numpy()))
+    with pytest.raises(ValueError):
+        e8.e8_decode_packed(codes, q, M, depth=0)
+
+
 def test_bf16_in_and_out(e8):
     """bf16 oracle = widen to float32, run the reference arithmetic, round the result to bf16."""
     torch.manual_seed(5)

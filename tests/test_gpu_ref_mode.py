@@ -37,3 +37,32 @@ def test_core_and_ref_modes_disagree_as_in_the_reference():
     ref, _ = HNLQ.create_e8_quantizer(q=4, M=2, beta=1.0, overload=False).encode(x)
     differ = (core.long() != ref.long()).any(dim=2).any(dim=1).float().mean()
     assert 0.1 < float(differ) < 0.7
+
+
+GC = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_coarse.npz"))
+
+
+@pytest.mark.parametrize("tag", ["b025", "b01", "q3m3"])
+def test_ref_coarse_to_fine_and_progressive_decode(tag):
+    from coset_b200.ref import HNLQ
+    beta, alpha, q, M, over = G[f"{tag}_params"]
+    M = int(M)
+    want = GC[f"{tag}_by_depth"]
+    n = want.shape[1]
+    digits = torch.from_numpy(G[f"{tag}_digits"][:n])
+    T = torch.from_numpy(G[f"{tag}_T"][:n])
+    h = HNLQ.create_e8_quantizer(q=int(q), M=M, beta=float(beta), alpha=float(alpha), overload=bool(over),
+                                 decoding="progressive")
+    prog = h.get_default_decoding(digits, T)
+    assert len(prog) == M
+    for depth in range(1, M + 1):
+        assert np.array_equal(prog[depth - 1].cpu().numpy(), want[depth - 1]), depth
+        assert np.array_equal(h.decode_with_depth(digits, T, depth).cpu().numpy(), want[depth - 1])
+    assert np.array_equal(h.decode_coarse_to_fine(digits, T).cpu().numpy(), want[M - 1])  # depth=None: full decode
+    # single-vector form
+    b_list = tuple(G[f"{tag}_digits"][5, m] for m in range(M))
+    assert np.array_equal(h.decode_coarse_to_fine(b_list, int(G[f"{tag}_T"][5]), depth=1), want[0][5])
+    with pytest.raises(ValueError):
+        h.decode_coarse_to_fine(digits, T, depth=M + 1)
+    with pytest.raises(ValueError):
+        h.decode_with_depth(digits, T, 0)
