@@ -43,6 +43,10 @@ SIGNATURES = {
     "coset_e8_ref_encode": [_vp, _i64, ctypes.c_double, ctypes.c_double, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp],
     "coset_e8_ref_decode": [_vp, _vp, _i64, ctypes.c_double, ctypes.c_double, _i32, _i32, _vp, _vp, _vp],
     "coset_e8_ref_decode_coarse": [_vp, _vp, _i64, ctypes.c_double, ctypes.c_double, _i32, _i32, _i32, _vp, _vp, _vp],
+    "coset_d4_projection": [_vp, _i64, _vp, _vp],
+    "coset_d4_quantize": [_vp, _i32, _vp, _i32, _i64, _i64, _f32, _vp, _i32, _vp],
+    "coset_d4_fake_quant_bwd": [_vp, _i32, _vp, _vp, _i64, _i64, _f32, _vp, _vp, _vp],
+    "coset_lattice_babai": [_vp, _i64, _i32, _vp, _vp, _f32, _vp, _vp],
     "coset_e8_dequant_gemm": [_vp, _vp, _i64, _i32, _i32, _vp, _i64, _i32, _vp, _vp, _i64, _vp, _vp],
     "coset_e8_fake_quant_bwd": [_vp, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _vp, _vp],
 }

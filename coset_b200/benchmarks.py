@@ -136,6 +136,37 @@ def bench_vlut():
                                   "frac": flops / (ms2 * 1e-3) / 1e12 / tf, "peaks": src}), flush=True)
 
 
+def bench_d4():
+    """D4 weight path clamp(projection(W beta) / beta) and Babai rounding on 2^26 blocks of 4."""
+    from . import _lib
+    from .core.babai import babai_project
+    from .core.d4 import D4Lattice
+    from .core.e8 import E8Lattice
+    hbm, _, src = peaks()
+    n = 1 << 26
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(n, 4, device="cuda", generator=g) * 0.02
+    beta = torch.full((n,), 25.0, device="cuda")
+    out = torch.empty_like(x)
+    L = _lib.lib()
+
+    def run():
+        rc = L.coset_d4_quantize(_lib.ptr(x), 0, _lib.ptr(beta), _lib.SCALE_MUL_TILE, n, 1, 2.0, _lib.ptr(out), 0, _lib.stream())
+        assert rc == 0
+
+    ms = cuda_time(run, iters=20)
+    by = n * 36
+    print(json.dumps({"bench": "d4_quantize", "blocks": n, "ms": ms, "GBps": by / (ms * 1e-3) / 1e9,
+                      "frac_of_hbm": by / (ms * 1e-3) / 1e9 / hbm, "bytes_per_block": 36, "peaks": src}), flush=True)
+    for name, lat, nb in (("d4", D4Lattice(device="cuda"), n), ("e8", E8Lattice(device="cuda"), n // 2)):
+        xb = x.view(nb, lat.d)
+        ms = cuda_time(lambda: babai_project(xb, lat, 0.25), iters=20)
+        by = nb * lat.d * 8
+        print(json.dumps({"bench": f"babai_{name}", "blocks": nb, "ms": ms, "GBps": by / (ms * 1e-3) / 1e9,
+                          "frac_of_hbm": by / (ms * 1e-3) / 1e9 / hbm, "note": "includes the output allocation of the Python call",
+                          "peaks": src}), flush=True)
+
+
 def bench_vlut_sharded():
     """Config-4 weight split along the output features over the ranks of a torchrun launch: every
     rank multiplies its [4096 / W, 4096] slice, one all-gather of the outputs follows."""
@@ -240,6 +271,8 @@ def main(argv=None):
         bench_qat()
     if which in ("vlut", "all"):
         bench_vlut()
+    if which in ("d4", "all"):
+        bench_d4()
     if which == "vlut_sharded":
         bench_vlut_sharded()
     if which in ("gradcomm", "all"):

@@ -213,9 +213,11 @@ class HNLQLinearQAT(nn.Module):
         self._weight_history = [] if enable_diagnostics else None
         self._quantization_errors = [] if enable_diagnostics else None
 
-        # The fused kernel implements the E8 quantiser; any other quantize_fn runs op by op.
+        # The fused kernels implement the E8 and the D4 quantiser; any other quantize_fn runs op by op.
+        from .d4.layers import d4_quantize as _fused_d4_fn
         from .e8.codecs import e8_quantize as _fused_fn
         self._fused = (quantize_fn is _fused_fn) and block_size == 8
+        self._fused_d4 = (quantize_fn is _fused_d4_fn) and block_size == 4
 
     # ------------------------------------------------------------------ weights
     def _initialize_weights(self):
@@ -301,8 +303,11 @@ class HNLQLinearQAT(nn.Module):
         bpt = self.blocks_per_row if self.tiling == "row" else 1
         if self._fused and W.is_cuda:
             W_q = e8_fake_quantize(W, beta, bpt, self.q, self.weight_clip_value, out_dtype)
-        elif self._fused:
-            raise ValueError("HNLQLinearQAT with the E8 quantiser needs its parameters on a CUDA device "
+        elif self._fused_d4 and W.is_cuda:
+            from .d4.layers import d4_fake_quantize
+            W_q = d4_fake_quantize(W, beta, bpt, self.weight_clip_value, out_dtype)
+        elif self._fused or self._fused_d4:
+            raise ValueError("HNLQLinearQAT with the E8 / D4 quantiser needs its parameters on a CUDA device "
                              "(coset_b200 has no CPU path); call .to('cuda')")
         else:
             W_q = self._quantize_weights_opwise(W, beta)

@@ -234,6 +234,36 @@ int coset_e8_ref_decode_coarse(const int32_t* digits, const int32_t* T, int64_t 
                                const double* dither_host, double* out, void* stream);
 
 /*
+ * D4 lattice (blocks of 4 values), the reference's second lattice behind the same layer.
+ *
+ * coset_d4_projection: D4Lattice.projection (coset/core/d4/lattice.py:111-146; g_x at :62-109 with
+ *   the same unused flip_negative mask as E8).  x, out: float32 [n_blocks, 4].
+ * coset_d4_quantize: weight path of the layer built by create_d4_hnlq_linear
+ *   (coset/core/d4/layers.py:15-68; coset/core/layers.py:429-463):
+ *   out = clamp(projection(x * scale[tile]) / scale[tile], +-clip) for COSET_SCALE_MUL_TILE,
+ *   out = clamp(projection(x), +-clip) for COSET_SCALE_NONE; clip <= 0 disables the clamp.
+ *   x / out: float32 or bf16 [n_blocks, 4]; blocks_per_tile counts blocks of 4.
+ * coset_d4_fake_quant_bwd: straight-through gradients of that graph (coset/core/layers.py:62-95);
+ *   the unclamped forward value is recomputed from w.  grad_beta may be NULL.
+ */
+int coset_d4_projection(const float* x, int64_t n_blocks, float* out, void* stream);
+int coset_d4_quantize(const void* x, int x_dtype, const float* scale, int scale_mode, int64_t n_blocks,
+                      int64_t blocks_per_tile, float clip, void* out, int out_dtype, void* stream);
+int coset_d4_fake_quant_bwd(const void* grad_out, int grad_dtype, const float* w, const float* beta,
+                            int64_t n_blocks, int64_t blocks_per_tile, float clip, float* grad_w,
+                            float* grad_beta, void* stream);
+
+/*
+ * Babai projection (pub/main.tex, algorithm "Babai projection onto E8"; weight path of
+ * ref/qat_auto.py:120-124): z = Ginv x, z_hat = round_half_even(z / step) * step, out = G z_hat.
+ * dim = 4 or 8; G_host / Ginv_host: dim x dim float32, row-major, basis vectors as columns
+ * (Lattice.G / Lattice.G_inv), read on the host.  x, out: float32 [n_blocks, dim].  Products and
+ * sums are rounded separately and accumulated left to right.
+ */
+int coset_lattice_babai(const float* x, int64_t n_blocks, int dim, const float* G_host,
+                        const float* Ginv_host, float step, float* out, void* stream);
+
+/*
  * Code-domain product for MANY tokens on the tcgen05 tensor cores: same result as
  * coset_e8_vlut_gemv (y = x * (decode(codes)/beta)^T + bias) with the weight tile decoded to bf16
  * in shared memory and multiplied by tcgen05.mma with the accumulator in tensor memory.

@@ -1,4 +1,4 @@
-"""ctypes/numpy front-end of the CPU oracle (oracle/e8_oracle.c).
+"""ctypes/numpy front-end of the CPU oracle (oracle/e8_oracle.c, oracle/d4_oracle.c).
 
 TEST INFRASTRUCTURE ONLY: imported by tests/, by __graft_entry__.smoke() and by bench.py's
 CPU-baseline legs.  Nothing under coset_b200/ may import this module.
@@ -19,8 +19,8 @@ _u32p = ctypes.POINTER(ctypes.c_uint32)
 
 def build(force=False):
     """Compile the C oracle with gcc (oracle/Makefile)."""
-    src = os.path.join(_HERE, "e8_oracle.c")
-    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+    srcs = [os.path.join(_HERE, f) for f in ("e8_oracle.c", "d4_oracle.c")]
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < max(os.path.getmtime(f) for f in srcs):
         subprocess.check_call(["make", "-C", _HERE, "-s"])
     return _SO
 
@@ -180,4 +180,41 @@ def ref_decode(digits, T, beta=1.0, alpha=1.0, q=4, dither=None, depth=None):
     lib().e8o_ref_decode_depth(digits.ctypes.data_as(_i32p), T.ctypes.data_as(_i32p), ctypes.c_int64(n),
                                ctypes.c_double(beta), ctypes.c_double(alpha), q, M, M if depth is None else int(depth),
                                d.ctypes.data_as(_f64p), out.ctypes.data_as(_f64p))
+    return out
+
+
+# ---- D4 lattice path and Babai projection (oracle/d4_oracle.c)
+def d4_projection(x):
+    x, xp = _f32(x)
+    out = np.empty_like(x)
+    lib().d4o_projection_rows(xp, ctypes.c_int64(x.shape[0]), out.ctypes.data_as(_f32p))
+    return out
+
+
+def d4_g_x(x):
+    x, xp = _f32(x)
+    out = np.empty_like(x)
+    lib().d4o_g_x_rows(xp, ctypes.c_int64(x.shape[0]), out.ctypes.data_as(_f32p))
+    return out
+
+
+def d4_fake_quant(w_blocks, beta, blocks_per_tile, clip=2.0):
+    """-> (clamped, unclipped) float32 [n, 4]."""
+    w, wp = _f32(w_blocks)
+    b, bp = _beta_arg(beta, 2)
+    wq = np.empty_like(w)
+    un = np.empty_like(w)
+    lib().d4o_fake_quant(wp, ctypes.c_int64(w.shape[0]), bp, ctypes.c_int64(blocks_per_tile), ctypes.c_float(clip),
+                         wq.ctypes.data_as(_f32p), un.ctypes.data_as(_f32p))
+    return wq, un
+
+
+def babai(x, G, Ginv, step=1.0):
+    """Babai rounding of the rows of x in the basis G (d x d, basis vectors as columns)."""
+    x, xp = _f32(x)
+    G, Gp = _f32(G)
+    Gi, Gip = _f32(Ginv)
+    out = np.empty_like(x)
+    lib().lato_babai(xp, ctypes.c_int64(x.shape[0]), int(x.shape[1]), Gp, Gip, ctypes.c_float(step),
+                     out.ctypes.data_as(_f32p))
     return out
