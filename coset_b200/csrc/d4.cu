@@ -9,9 +9,11 @@
 // A D4 block is 4 values.  The search is short (4 roundings, a parity test, one flip), so these
 // kernels are bound by HBM: 16 B in + 16 B out per block.  Each thread owns two consecutive
 // blocks (one 32-byte row) so that accesses stay 128-bit and fully coalesced; an odd last block is
-// handled by the last thread alone.  Every operation is the reference's float32 operation in the
-// reference's order (__f*_rn intrinsics are never contracted), so results are bit-identical.
+// handled by the last thread alone.  Every value that reaches the output is produced by the reference's
+// float32 operations in the reference's order (__f*_rn intrinsics are never contracted) or by a
+// sequence shown to round identically, so results are bit-identical.
 #include <cuda_bf16.h>
+#include <math.h>
 
 #include "common.cuh"
 #include "e8_io.cuh"
@@ -51,6 +53,13 @@ struct Row4<1> {
     }
 };
 
+// custom_round with the nudge taken as copysign(2^-23, x): for x = +-0 the reference's nudge is 0,
+// here it is +-2^-23, and both give floor(0.5 -+ tiny) = 0, so the results agree for every input.
+__device__ __forceinline__ float d4_round(float x) {
+    float nudge = __uint_as_float((__float_as_uint(x) & 0x80000000u) | 0x34000000u);
+    return floorf(__fadd_rn(__fsub_rn(x, nudge), 0.5f));
+}
+
 // D4Lattice.projection on one block: f = custom_round(x); if sum(f) is odd (python float `% 2`),
 // the coordinate with the largest |x - f| (first index on ties; NaN counts as largest) moves by
 // +1 when x_k >= 0 and f_k < x_k and by -1 in every other case -- the reference computes a
@@ -59,10 +68,14 @@ __device__ __forceinline__ void d4_projection(const float (&x)[4], float (&y)[4]
     float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        y[i] = e8::custom_round(x[i]);
+        y[i] = d4_round(x[i]);
         s = __fadd_rn(s, y[i]);
     }
-    if (fmodf(s, 2.0f) == 0.0f) return;  // NaN / inf sums take the g_x branch, as `% 2 == 0` is false
+    // python float `s % 2 == 0`: integer parity below 2^24, every finite float from 2^24 up is an
+    // even integer, and NaN / inf compare false (those rows take the g_x branch like the reference)
+    float as = fabsf(s);
+    bool even = as < 16777216.0f ? ((__float2int_rn(s) & 1) == 0) : (as < __int_as_float(0x7f800000));
+    if (even) return;
     int k = 0;
     float best = fabsf(__fsub_rn(x[0], y[0]));
     bool done = best != best;
@@ -89,9 +102,30 @@ __device__ __forceinline__ void d4_fake_quant_block(const float (&w)[4], float b
 #pragma unroll
     for (int i = 0; i < 4; ++i) xs[i] = SCALED ? __fmul_rn(w[i], beta) : w[i];
     d4_projection(xs, p);
+    if (SCALED) {
+        // p / beta: for integer numerators up to 64 the sequence q0 = p r, q = fma(fma(-q0, beta, p), r, q0)
+        // with r = RN(1 / beta) is the correctly rounded quotient for every float32 significand of
+        // beta (checked exhaustively on the CPU) while beta stays far from the exponent limits;
+        // anything else takes the IEEE division.
+        float amax = fmaxf(fmaxf(fabsf(p[0]), fabsf(p[1])), fmaxf(fabsf(p[2]), fabsf(p[3])));
+        float ab = fabsf(beta);
+        if (amax <= 64.0f && ab > 1e-18f && ab < 1e18f) {
+            float r = __frcp_rn(beta);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float q0 = __fmul_rn(p[i], r);
+                u[i] = __fmaf_rn(__fmaf_rn(-q0, beta, p[i]), r, q0);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) u[i] = __fdiv_rn(p[i], beta);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) u[i] = p[i];
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        u[i] = SCALED ? __fdiv_rn(p[i], beta) : p[i];
         float v = u[i];
         c[i] = (clip > 0.0f && v == v) ? fminf(fmaxf(v, -clip), clip) : v;  // torch.clamp keeps NaN
     }
@@ -195,7 +229,7 @@ struct Basis {
 
 template <int D>
 __global__ void __launch_bounds__(kThreads)
-k_babai(const float* __restrict__ x, int64_t n, Basis basis, float step, float* __restrict__ out) {
+k_babai(const float* __restrict__ x, int64_t n, Basis basis, float step, float inv_step, float* __restrict__ out) {
     int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (b >= n) return;
     float v[D], z[D], y[D];
@@ -210,7 +244,9 @@ k_babai(const float* __restrict__ x, int64_t n, Basis basis, float step, float* 
         float acc = 0.0f;
 #pragma unroll
         for (int i = 0; i < D; ++i) acc = __fadd_rn(acc, __fmul_rn(basis.Ginv[a * D + i], v[i]));
-        z[a] = __fmul_rn(rintf(__fdiv_rn(acc, step)), step);
+        // inv_step != 0: step is a power of two, so the product equals the IEEE quotient
+        float t = inv_step != 0.0f ? __fmul_rn(acc, inv_step) : __fdiv_rn(acc, step);
+        z[a] = __fmul_rn(rintf(t), step);
     }
 #pragma unroll
     for (int a = 0; a < D; ++a) {
@@ -307,9 +343,12 @@ int coset_lattice_babai(const float* x, int64_t n_blocks, int dim, const float* 
         basis.Ginv[i] = Ginv_host[i];
     }
     for (int i = dim * dim; i < 64; ++i) basis.G[i] = basis.Ginv[i] = 0.0f;
+    int exp2 = 0;
+    const bool pow2 = frexpf(step, &exp2) == 0.5f && exp2 > -100 && exp2 < 100;
+    const float inv_step = pow2 ? 1.0f / step : 0.0f;
     unsigned grid = (unsigned)((n_blocks + kThreads - 1) / kThreads);
-    if (dim == 4) k_babai<4><<<grid, kThreads, 0, (cudaStream_t)stream>>>(x, n_blocks, basis, step, out);
-    else k_babai<8><<<grid, kThreads, 0, (cudaStream_t)stream>>>(x, n_blocks, basis, step, out);
+    if (dim == 4) k_babai<4><<<grid, kThreads, 0, (cudaStream_t)stream>>>(x, n_blocks, basis, step, inv_step, out);
+    else k_babai<8><<<grid, kThreads, 0, (cudaStream_t)stream>>>(x, n_blocks, basis, step, inv_step, out);
     return check_launch("lattice_babai");
 }
 

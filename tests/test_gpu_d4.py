@@ -189,3 +189,15 @@ def test_babai(name, step):
     assert torch.equal(xg.grad, torch.ones_like(xg))
     with pytest.raises(ValueError):
         babai_project(torch.zeros(2, 5, device="cuda"), lat, step)
+
+
+def test_babai_non_power_of_two_step_vs_oracle():
+    """A step that is not a power of two takes the IEEE division, like the CPU restatement."""
+    from coset_b200.core.babai import babai_project
+    from coset_b200.core.e8 import E8Lattice
+    lat = E8Lattice(device="cuda")
+    x = G["babai_e8_x"]
+    for step in (0.3, 0.0059375):
+        got = babai_project(dev(x), lat, step).cpu().numpy()
+        want = O.babai(x, lat.G.cpu().numpy(), lat.G_inv.cpu().numpy(), step)
+        assert np.array_equal(bits(got), bits(want))
