@@ -39,7 +39,7 @@ BETA_LITERAL = 0.021440971642732620
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one encode launch, from the ncu capture
 # summarised in profiles/, scaled to the full launch by the number of blocks.
-ENCODE_TRAFFIC_BYTES_PER_LAUNCH = 1.2756e9  # 8 x (151.15 + 8.30) MB measured on 2^22 blocks, see profiles/codec_q4m2_bulk_fp32.md
+ENCODE_TRAFFIC_BYTES_PER_LAUNCH = 1.2725e9  # 8 x (151.03 + 8.03) MB measured on 2^22 blocks, see profiles/codec_q4m2_bulk_fp32.md
 
 
 def make_values(n_values, seed):
@@ -350,7 +350,7 @@ def main():
             "ms_per_step": total_ms / args.steps,
             "gpu_launches": 2 * args.steps,
             "frac_of_hbm_peak": value / world / peak,
-            "roofline": {"bound": "hbm", "kernel": "k_encode_q4m2 (dominant: %.0f%% of the step)" % (100 * per[0] / (per[0] + per[1])),
+            "roofline": {"bound": "hbm", "kernel": "k_encode_q4m2_queued (dominant: %.0f%% of the step)" % (100 * per[0] / (per[0] + per[1])),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": ENCODE_TRAFFIC_BYTES_PER_LAUNCH * n / N_BLOCKS, "algorithmic_bytes_per_launch": n * BYTES_PER_BLOCK_ENC,
                          "peak_source": peak_src, "ms_per_launch": enc_ms,
