@@ -39,7 +39,7 @@ BETA_LITERAL = 0.021440971642732620
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one encode launch, from the ncu capture
 # summarised in profiles/, scaled to the full launch by the number of blocks.
-ENCODE_TRAFFIC_BYTES_PER_LAUNCH = 1.2725e9  # 8 x (151.03 + 8.03) MB measured on 2^22 blocks, see profiles/codec_q4m2_bulk_fp32.md
+ENCODE_TRAFFIC_BYTES_PER_LAUNCH = 1.2725e9  # 8 x (151.03 + 8.03) MB: dram read + write of one ncu capture on 2^22 blocks, scaled to 2^25
 
 
 def make_values(n_values, seed):
@@ -76,6 +76,7 @@ class ClockSampler:
     def __init__(self, index, period_s=0.002):
         import threading
         self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._mark = 0
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -105,6 +106,10 @@ class ClockSampler:
         except Exception as e:  # NVML missing: the line then carries "clocks": null
             self.error = repr(e)
 
+    def mark(self):
+        """Start of the timed steps: samples before this belong to the warm-up (same load)."""
+        self._mark = len(self.samples)
+
     def stop(self):
         if self._thread is None:
             return None
@@ -112,7 +117,13 @@ class ClockSampler:
         self._thread.join(timeout=2)
         if not self.samples:
             return None
-        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+        timed = self.samples[self._mark:]
+        # an NVML query takes milliseconds; when the timed steps are shorter than three queries the
+        # warm-up steps (the same kernels on the same data, back to back) are included and named
+        window = "timed steps" if len(timed) >= 3 else "warm-up + timed steps (same load, back to back)"
+        self.samples = timed if len(timed) >= 3 else self.samples
+        self.window = window
+        return {"window": window, "sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
                 "samples": len(self.samples)}
 
 
@@ -240,13 +251,15 @@ def main():
         e8_decode_packed(codes, 4, 2, scale=beta, scale_mode=MT, blocks_per_tile=1, out=xhat)
 
     # ---- timed region: K steps of (encode, decode), inputs resident in HBM
+    sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(args.warmup):
         enc(); dec()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
     torch.cuda.synchronize()
+    if sampler:
+        sampler.mark()
     total_ms, per = time_kernels([enc, dec], args.steps, 0)
     torch.cuda.synchronize()
     if world > 1:
