@@ -339,10 +339,12 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
 // Two blocks per thread (kThreads apart, so every access stays coalesced): both codes are
 // loaded before the first table lookup, which doubles the gathers in flight per thread.
 constexpr int kDecPerThread = 2;
-template <int DT, int MODE>
+// TABLE is `uint2` (8-byte entries) or `uint32_t` (packed 4-byte entries, used for float32 output,
+// where the kernel is bound by the gathers and not by instruction issue).
+template <int DT, int MODE, typename TABLE>
 __global__ void __launch_bounds__(kThreads)
 k_decode_q4m2(const uint32_t* __restrict__ codes, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
-              const uint2* __restrict__ table, void* __restrict__ out) {
+              const TABLE* __restrict__ table, void* __restrict__ out) {
     int64_t base = (int64_t)blockIdx.x * (kThreads * kDecPerThread) + threadIdx.x;
     uint32_t code[kDecPerThread];
     float s[kDecPerThread];
@@ -366,7 +368,7 @@ k_decode_q4m2(const uint32_t* __restrict__ codes, const float* __restrict__ scal
 
 // Residual table of the q=4 decoder, produced by the literal float32 decoder itself:
 // entry[w] = 2 * (G b - 4 Q(G b / 4)) + 7 for the 16-bit level word w, as 8 unsigned bytes.
-__global__ void k_build_table_q4(uint2* __restrict__ table) {
+__global__ void k_build_table_q4(uint2* __restrict__ table, uint32_t* __restrict__ packed, int* __restrict__ bad) {
     int w = blockIdx.x * blockDim.x + threadIdx.x;
     if (w >= 65536) return;
     int d[8];
@@ -380,6 +382,21 @@ __global__ void k_build_table_q4(uint2* __restrict__ table) {
         hi |= ((uint32_t)((__float2int_rn(__fmul_rn(r[i + 4], 2.0f)) + e8::kTableBias) & 0xff)) << (8 * i);
     }
     table[w] = make_uint2(lo, hi);
+    // packed entry (layout at e8::biased_bytes_q4m2); `bad` counts residuals that do not fit it
+    int t[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t[i] = __float2int_rn(__fmul_rn(r[i], 2.0f));
+    const int p = t[0] & 1;
+    uint32_t e = (uint32_t)p << 31;
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int nib = (t[i] - p + (i < 7 ? e8::kNibbleBias : e8::kNibbleBias7)) >> 1;
+        ok = ok && ((t[i] & 1) == p) && nib >= 0 && nib <= (i < 7 ? 15 : 7);
+        e |= ((uint32_t)nib & 0xfu) << (4 * i);
+    }
+    if (!ok) atomicAdd(bad, 1);
+    packed[w] = e;
 }
 
 // ---------------------------------------------------------------- digit views
@@ -439,18 +456,36 @@ const uint2* residual_table_q4(cudaStream_t stream) {
     if (dev < 0 || dev >= 64) { fail(COSET_E_STATE, "device index %d out of range", dev); return nullptr; }
     std::lock_guard<std::mutex> lock(mu);
     if (!tables[dev]) {
-        uint2* t = nullptr;
-        if (check_cuda(cudaMalloc(&t, 65536 * sizeof(uint2)), "cudaMalloc(residual table)")) return nullptr;
+        uint2* t = nullptr;  // 65536 x 8 B, then 65536 x 4 B packed, then the builder's self-check word
+        if (check_cuda(cudaMalloc(&t, 65536 * (sizeof(uint2) + sizeof(uint32_t)) + 16), "cudaMalloc(residual table)")) return nullptr;
+        uint32_t* packed = reinterpret_cast<uint32_t*>(t + 65536);
+        int* bad = reinterpret_cast<int*>(packed + 65536);
+        int bad_host = -1;
         // Built on the caller's stream: every later use on any stream must see it complete, so
         // the one-time build synchronises that stream.
-        k_build_table_q4<<<65536 / 256, 256, 0, stream>>>(t);
-        if (check_launch("k_build_table_q4") || check_cuda(cudaStreamSynchronize(stream), "table build")) {
+        bool failed = check_cuda(cudaMemsetAsync(bad, 0, sizeof(int), stream), "table build") != 0;
+        if (!failed) {
+            k_build_table_q4<<<65536 / 256, 256, 0, stream>>>(t, packed, bad);
+            failed = check_launch("k_build_table_q4") ||
+                     check_cuda(cudaMemcpyAsync(&bad_host, bad, sizeof(int), cudaMemcpyDeviceToHost, stream), "table build") ||
+                     check_cuda(cudaStreamSynchronize(stream), "table build");
+        }
+        if (!failed && bad_host != 0) {
+            fail(COSET_E_STATE, "residual table: %d entries do not fit the packed layout", bad_host);
+            failed = true;
+        }
+        if (failed) {
             cudaFree(t);
             return nullptr;
         }
         tables[dev] = t;
     }
     return tables[dev];
+}
+
+const uint32_t* residual_table_q4_packed(cudaStream_t stream) {
+    const uint2* t = residual_table_q4(stream);
+    return t ? reinterpret_cast<const uint32_t*>(t + 65536) : nullptr;
 }
 
 }  // namespace coset
@@ -520,9 +555,14 @@ int coset_e8_decode(const void* codes, const float* scale, int scale_mode, int64
     unsigned grid = grid_for(n_blocks);
     if (q == 4 && M == 2) {
         const uint2* table = residual_table_q4(st);
-        if (!table) return COSET_E_STATE;
+        const uint32_t* packed = residual_table_q4_packed(st);
+        if (!table || !packed) return COSET_E_STATE;
         unsigned grid2 = (unsigned)((n_blocks + kThreads * kDecPerThread - 1) / (kThreads * kDecPerThread));
-        DISPATCH_DT(out_dtype, DT, DISPATCH_MODE(scale_mode, (k_decode_q4m2<DT, MODE><<<grid2, kThreads, 0, st>>>((const uint32_t*)codes, scale, td, n_blocks, table, out))))
+        if (out_dtype == COSET_DTYPE_F32) {
+            DISPATCH_MODE(scale_mode, (k_decode_q4m2<0, MODE, uint32_t><<<grid2, kThreads, 0, st>>>((const uint32_t*)codes, scale, td, n_blocks, packed, out)))
+        } else {
+            DISPATCH_MODE(scale_mode, (k_decode_q4m2<1, MODE, uint2><<<grid2, kThreads, 0, st>>>((const uint32_t*)codes, scale, td, n_blocks, table, out)))
+        }
     } else if (q <= 4) {
         DISPATCH_DT(out_dtype, DT, DISPATCH_MODE(scale_mode, (k_decode_generic<DT, MODE, 2><<<grid, kThreads, 0, st>>>(codes, scale, td, n_blocks, q, M, out))))
     } else {

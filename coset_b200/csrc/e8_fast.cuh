@@ -252,6 +252,42 @@ __device__ __forceinline__ void decode_q4m2_twice(uint32_t code, const uint2* __
     v2[7] = __fsub_rn(biased_byte_to_float<3>(hi), kOff);
 }
 
+// Packed form of the same table: 4 bytes per level word.  With t_i = 2 r_i(b) (an integer in
+// [-7, 11]; |t_7| <= 5), all t_i of one entry have the same parity p (integer or half-integer
+// coset), so
+//     nibble i (bits 4i..4i+3) = (t_i - p + 8) / 2  in [0, 9]   for i < 7,
+//     nibble 7 low 3 bits      = (t_7 - p + 6) / 2  in [0, 5],  bit 31 = p.
+// With two levels, 2 x_hat_i = t0_i + 4 t1_i = 2 (n0_i + 4 n1_i) + (p0 + 4 p1) - 5 bias_i; even and
+// odd nibbles are widened to byte lanes, so four coordinates share each 32-bit multiply-add and the
+// byte B_i = 2 (n0_i + 4 n1_i) + p0 + 4 p1 stays below 96.
+constexpr int kNibbleBias = 8, kNibbleBias7 = 6;
+
+// Byte lanes B of the two packed entries of one code: `even` holds coordinates 0, 2, 4, 6 and `odd`
+// coordinates 1, 3, 5, 7; coordinate i is B_i - 40 (B_7 - 30) = twice the reconstruction.
+__device__ __forceinline__ void biased_bytes_q4m2(uint32_t e0, uint32_t e1, uint32_t& even, uint32_t& odd) {
+    const uint32_t s_even = (e0 & 0x0f0f0f0fu) + 4u * (e1 & 0x0f0f0f0fu);
+    const uint32_t s_odd = ((e0 >> 4) & 0x070f0f0fu) + 4u * ((e1 >> 4) & 0x070f0f0fu);
+    const uint32_t rep = ((e0 >> 31) + 4u * (e1 >> 31)) * 0x01010101u;  // p0 + 4 p1 in every byte lane
+    even = 2u * s_even + rep;
+    odd = 2u * s_odd + rep;
+}
+
+__device__ __forceinline__ void decode_q4m2_twice(uint32_t code, const uint32_t* __restrict__ packed, float (&v2)[8]) {
+    const uint32_t e0 = __ldg(packed + (code & 0xffffu));
+    const uint32_t e1 = __ldg(packed + (code >> 16));
+    uint32_t even, odd;
+    biased_bytes_q4m2(e0, e1, even, odd);
+    const float kOff = 12582912.0f + 5.0f * kNibbleBias, kOff7 = 12582912.0f + 5.0f * kNibbleBias7;
+    v2[0] = __fsub_rn(biased_byte_to_float<0>(even), kOff);
+    v2[1] = __fsub_rn(biased_byte_to_float<0>(odd), kOff);
+    v2[2] = __fsub_rn(biased_byte_to_float<1>(even), kOff);
+    v2[3] = __fsub_rn(biased_byte_to_float<1>(odd), kOff);
+    v2[4] = __fsub_rn(biased_byte_to_float<2>(even), kOff);
+    v2[5] = __fsub_rn(biased_byte_to_float<2>(odd), kOff);
+    v2[6] = __fsub_rn(biased_byte_to_float<3>(even), kOff);
+    v2[7] = __fsub_rn(biased_byte_to_float<3>(odd), kOff7);
+}
+
 // x_hat = v2 / 2 with the reference's output scaling applied as the same IEEE operation:
 //   MODE 0: x_hat                      (exact halving)
 //   MODE 1: x_hat * s                  (coset/core/e8/codecs.py:175)   = RN(v2 * (s/2))
