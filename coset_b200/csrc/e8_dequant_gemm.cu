@@ -144,13 +144,14 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
 
     const int KT = K / BK;
     if (warp < PRODUCERS / 32) {
-        // Each producer thread owns 2 (row, chunk) slots of every tile.  Codes and scales of step
-        // kt+1 are loaded into registers before step kt is decoded; activations go global->shared
-        // with cp.async and overlap the table gathers of the decode.
+        // Each producer thread owns 2 (row, chunk) slots of every tile.  Activations go
+        // global->shared with cp.async; codes, scales and table entries travel through registers.
         constexpr int SLOTS = (BN * 8) / PRODUCERS;
         uint32_t code_n[SLOTS];
         float beta_n[SLOTS];
-        auto fetch = [&](int kt) {
+        uint2 lo_e[SLOTS], hi_e[SLOTS];  // residual-table entries of the two level words
+        float beta_e[SLOTS];
+        auto fetch_codes = [&](int kt) {
 #pragma unroll
             for (int j = 0; j < SLOTS; ++j) {
                 int idx = tid + j * PRODUCERS, row = idx >> 3, c = idx & 7;
@@ -164,39 +165,67 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
                 }
             }
         };
-        fetch(0);
+        auto fetch_entries = [&]() {  // of the codes in code_n; their scales move along
+#pragma unroll
+            for (int j = 0; j < SLOTS; ++j) {
+                lo_e[j] = __ldg(table + (code_n[j] & 0xffffu));
+                hi_e[j] = __ldg(table + (code_n[j] >> 16));
+                beta_e[j] = beta_n[j];
+            }
+        };
+        // Per-slot constants of the K loop: swizzled offset inside a tile, source row of every
+        // activation sub-tile (rows beyond T keep a valid address and copy 0 bytes = zero fill).
+        uint32_t slot_off[SLOTS];
+        const __nv_bfloat16* a_src[MSUB][SLOTS];
+        uint32_t a_bytes[MSUB][SLOTS];
+#pragma unroll
+        for (int j = 0; j < SLOTS; ++j) {
+            int idx = tid + j * PRODUCERS, row = idx >> 3, c = idx & 7;
+            slot_off[j] = swizzled_chunk_offset(row, c);
+#pragma unroll
+            for (int a = 0; a < MSUB; ++a) {
+                int tok = tok0 + a * BM + row;
+                int tok_c = tok < T ? tok : T - 1;
+                a_src[a][j] = x + (int64_t)tok_c * ldx + c * 8;
+                a_bytes[a][j] = tok < T ? 16u : 0u;
+            }
+        }
+        // Register pipeline over K steps: codes run two steps ahead of the decode and their table
+        // entries one step ahead, so neither the code load nor the dependent gathers sit between
+        // the "stage is free" wait and the shared-memory stores of a step.
+        fetch_codes(0);
+        fetch_entries();
+        if (KT > 1) fetch_codes(1);
         for (int kt = 0; kt < KT; ++kt) {
             const int s = kt % STAGES;
-            uint32_t code_c[SLOTS];
+            uint2 lo_c[SLOTS], hi_c[SLOTS];
             float beta_c[SLOTS];
 #pragma unroll
-            for (int j = 0; j < SLOTS; ++j) { code_c[j] = code_n[j]; beta_c[j] = beta_n[j]; }
-            if (kt + 1 < KT) fetch(kt + 1);
+            for (int j = 0; j < SLOTS; ++j) { lo_c[j] = lo_e[j]; hi_c[j] = hi_e[j]; beta_c[j] = beta_e[j]; }
+            if (kt + 1 < KT) fetch_entries();      // step kt+1: its codes arrived during step kt-1
+            if (kt + 2 < KT) fetch_codes(kt + 2);
             if (kt >= STAGES) ok = mbar_wait(bar_base + 8 * s, (uint32_t)((kt / STAGES - 1) & 1)) && ok;
             const uint32_t stage_addr = base + s * STAGE_BYTES;
             uint8_t* b_gen = gen + s * STAGE_BYTES + MSUB * TILE_BYTES;
-            for (int a = 0; a < n_sub; ++a) {
 #pragma unroll
-                for (int j = 0; j < SLOTS; ++j) {
-                    int idx = tid + j * PRODUCERS, row = idx >> 3, c = idx & 7;
-                    int tok = tok0 + a * BM + row;
-                    int tok_c = tok < T ? tok : T - 1;  // keep the address valid; 0 source bytes -> zero fill
-                    cp_async16(stage_addr + a * TILE_BYTES + swizzled_chunk_offset(row, c),
-                               x + (int64_t)tok_c * ldx + (int64_t)kt * BK + c * 8, tok < T ? 16u : 0u);
+            for (int a = 0; a < MSUB; ++a) {
+                if (a < n_sub && kt < 2) {
+#pragma unroll
+                    for (int j = 0; j < SLOTS; ++j)
+                        cp_async16(stage_addr + a * TILE_BYTES + slot_off[j], a_src[a][j] + (int64_t)kt * BK, a_bytes[a][j]);
                 }
             }
 #pragma unroll
             for (int j = 0; j < SLOTS; ++j) {
-                int idx = tid + j * PRODUCERS, row = idx >> 3, c = idx & 7;
                 // weights are rounded to bf16 here, so the scale is applied as one multiply by
                 // 0.5 / beta (relative error 2^-23, far below the bf16 rounding) instead of the
                 // exact IEEE division the float32 paths use; rows beyond N hold code 0 = weight 0
                 float half_inv = MODE == 2 ? __fdividef(0.5f, beta_c[j]) : 0.5f;
                 float v2[8];
-                e8::decode_q4m2_twice(code_c[j], table, v2);
+                e8::twice_from_entries(lo_c[j], hi_c[j], v2);
                 uint4 v = make_uint4(pack_bf16x2(v2[0] * half_inv, v2[1] * half_inv), pack_bf16x2(v2[2] * half_inv, v2[3] * half_inv),
                                      pack_bf16x2(v2[4] * half_inv, v2[5] * half_inv), pack_bf16x2(v2[6] * half_inv, v2[7] * half_inv));
-                *reinterpret_cast<uint4*>(b_gen + swizzled_chunk_offset(row, c)) = v;
+                *reinterpret_cast<uint4*>(b_gen + slot_off[j]) = v;
             }
             asm volatile("cp.async.wait_all;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA

@@ -237,9 +237,8 @@ __device__ __forceinline__ float biased_byte_to_float(uint32_t v) {
 }
 
 // Twice the reconstruction (an integer in [-35, 55]) of every coordinate, as exact floats.
-__device__ __forceinline__ void decode_q4m2_twice(uint32_t code, const uint2* __restrict__ table, float (&v2)[8]) {
-    uint2 t0 = __ldg(table + (code & 0xffffu));
-    uint2 t1 = __ldg(table + (code >> 16));
+// twice_from_entries: the same from the two table entries, already loaded.
+__device__ __forceinline__ void twice_from_entries(uint2 t0, uint2 t1, float (&v2)[8]) {
     uint32_t lo = t0.x + 4u * t1.x, hi = t0.y + 4u * t1.y;
     const float kOff = 12582912.0f + 5.0f * kTableBias;
     v2[0] = __fsub_rn(biased_byte_to_float<0>(lo), kOff);
@@ -250,6 +249,10 @@ __device__ __forceinline__ void decode_q4m2_twice(uint32_t code, const uint2* __
     v2[5] = __fsub_rn(biased_byte_to_float<1>(hi), kOff);
     v2[6] = __fsub_rn(biased_byte_to_float<2>(hi), kOff);
     v2[7] = __fsub_rn(biased_byte_to_float<3>(hi), kOff);
+}
+
+__device__ __forceinline__ void decode_q4m2_twice(uint32_t code, const uint2* __restrict__ table, float (&v2)[8]) {
+    twice_from_entries(__ldg(table + (code & 0xffffu)), __ldg(table + (code >> 16)), v2);
 }
 
 // Packed form of the same table: 4 bytes per level word.  With t_i = 2 r_i(b) (an integer in
