@@ -209,7 +209,7 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
             uint8_t* b_gen = gen + s * STAGE_BYTES + MSUB * TILE_BYTES;
 #pragma unroll
             for (int a = 0; a < MSUB; ++a) {
-                if (a < n_sub && kt < 2) {
+                if (a < n_sub) {
 #pragma unroll
                     for (int j = 0; j < SLOTS; ++j)
                         cp_async16(stage_addr + a * TILE_BYTES + slot_off[j], a_src[a][j] + (int64_t)kt * BK, a_bytes[a][j]);
