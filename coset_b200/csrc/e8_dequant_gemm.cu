@@ -232,20 +232,26 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
             __syncwarp();
             if (lane == 0) mbar_arrive(full_base + 8 * s);
         }
-    } else if (lane == 0) {
+    } else {
+        // MMA warp: all 32 lanes follow the loop together (a lane left spinning on another barrier
+        // would share this warp's issue slots with the lane that feeds the tensor core); lane 0
+        // issues the MMAs and the commits.
         for (int kt = 0; kt < KT; ++kt) {
             const int s = kt % STAGES;
             ok = mbar_wait(full_base + 8 * s, (uint32_t)((kt / STAGES) & 1)) && ok;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t stage_addr = base + s * STAGE_BYTES, b_addr = stage_addr + MSUB * TILE_BYTES;
-            for (int a = 0; a < n_sub; ++a) {
+            if (lane == 0) {
+                const uint32_t stage_addr = base + s * STAGE_BYTES, b_addr = stage_addr + MSUB * TILE_BYTES;
+                for (int a = 0; a < n_sub; ++a) {
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k)  // 16 bf16 = 32 bytes along K inside the 128-byte swizzle row
-                    umma_f16(tmem_d + (uint32_t)(a * BN), umma_desc(stage_addr + a * TILE_BYTES + k * 32), umma_desc(b_addr + k * 32),
-                             kIdesc, (kt > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / 16; ++k)  // 16 bf16 = 32 bytes along K inside the 128-byte swizzle row
+                        umma_f16(tmem_d + (uint32_t)(a * BN), umma_desc(stage_addr + a * TILE_BYTES + k * 32), umma_desc(b_addr + k * 32),
+                                 kIdesc, (kt > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(bar_base + 8 * s);            // stage s may be overwritten once these MMAs retire
+                if (kt == KT - 1) umma_commit(done_bar);  // ... and the accumulators are complete
             }
-            umma_commit(bar_base + 8 * s);            // stage s may be overwritten once these MMAs retire
-            if (kt == KT - 1) umma_commit(done_bar);  // ... and the accumulators are complete
+            __syncwarp();
         }
     }
     if (!ok && status) atomicExch(status, 1);
