@@ -4,7 +4,8 @@
 // One CTA owns a 512 (tokens) x 128 (output features) tile of y: four 128 x 128 accumulators
 // that fill the SM's tensor memory, so that every decoded weight tile is used by four MMAs.
 // Per 64-wide K step
-//   * up to four activation tiles A (128 x 64 bf16 each) are copied to shared memory (cp.async),
+//   * up to four activation tiles A (128 x 64 bf16 each) are copied to shared memory by TMA
+//     (cp.async.bulk.tensor.2d, one elected thread, completion counted on the stage's "full" mbarrier),
 //   * the weight tile      B (128 x 64 bf16) is DECODED into shared memory: one thread turns one
 //     packed E8 code (4 B) plus its scale into eight bf16 weights = one 16-byte chunk,
 // both in the K-major SWIZZLE_128B layout the UMMA shared-memory descriptor describes
@@ -18,6 +19,7 @@
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel records an error code, still frees
 // its tensor memory and returns.  No cluster features, no multicast, no peer memory.
+#include <cuda.h>
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -56,9 +58,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// 16-byte asynchronous global->shared copy; src_bytes = 0 writes zeros (rows beyond T)
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+// Adds `bytes` to the transaction count the barrier's current phase waits for (no arrival).
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// TMA: one 64 (K) x 128 (tokens) bf16 box of x -> shared memory in the 128-byte swizzle; rows beyond
+// T are filled with zeros.  k0 * 2 bytes is a multiple of 128, so the 16-byte rule on the inner
+// coordinate holds.  No multicast: the box lands in this CTA only.
+__device__ __forceinline__ void tma_load_a(uint32_t dst, const CUtensorMap* map, int k0, int tok, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(k0), "r"(tok), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -107,7 +117,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 template <int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ beta, e8::TileDiv td, int N, int K,
-               const __nv_bfloat16* __restrict__ x, int64_t ldx, int T, const float* __restrict__ bias,
+               const __grid_constant__ CUtensorMap x_map, int T, const float* __restrict__ bias,
                const uint2* __restrict__ table, float* __restrict__ y, int64_t ldy, int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -144,8 +154,8 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
 
     const int KT = K / BK;
     if (warp < PRODUCERS / 32) {
-        // Each producer thread owns 2 (row, chunk) slots of every tile.  Activations go
-        // global->shared with cp.async; codes, scales and table entries travel through registers.
+        // Each producer thread owns 2 (row, chunk) slots of the weight tile; codes, scales and table
+        // entries travel through registers.  Thread 0 also starts the TMA copies of the activations.
         constexpr int SLOTS = (BN * 8) / PRODUCERS;
         uint32_t code_n[SLOTS];
         float beta_n[SLOTS];
@@ -173,22 +183,12 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
                 beta_e[j] = beta_n[j];
             }
         };
-        // Per-slot constants of the K loop: swizzled offset inside a tile, source row of every
-        // activation sub-tile (rows beyond T keep a valid address and copy 0 bytes = zero fill).
+        // Per-slot constant of the K loop: swizzled offset inside the weight tile.
         uint32_t slot_off[SLOTS];
-        const __nv_bfloat16* a_src[MSUB][SLOTS];
-        uint32_t a_bytes[MSUB][SLOTS];
 #pragma unroll
         for (int j = 0; j < SLOTS; ++j) {
             int idx = tid + j * PRODUCERS, row = idx >> 3, c = idx & 7;
             slot_off[j] = swizzled_chunk_offset(row, c);
-#pragma unroll
-            for (int a = 0; a < MSUB; ++a) {
-                int tok = tok0 + a * BM + row;
-                int tok_c = tok < T ? tok : T - 1;
-                a_src[a][j] = x + (int64_t)tok_c * ldx + c * 8;
-                a_bytes[a][j] = tok < T ? 16u : 0u;
-            }
         }
         // Register pipeline over K steps: codes run two steps ahead of the decode and their table
         // entries one step ahead, so neither the code load nor the dependent gathers sit between
@@ -207,13 +207,10 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
             if (kt >= STAGES) ok = mbar_wait(bar_base + 8 * s, (uint32_t)((kt / STAGES - 1) & 1)) && ok;
             const uint32_t stage_addr = base + s * STAGE_BYTES;
             uint8_t* b_gen = gen + s * STAGE_BYTES + MSUB * TILE_BYTES;
-#pragma unroll
-            for (int a = 0; a < MSUB; ++a) {
-                if (a < n_sub) {
-#pragma unroll
-                    for (int j = 0; j < SLOTS; ++j)
-                        cp_async16(stage_addr + a * TILE_BYTES + slot_off[j], a_src[a][j] + (int64_t)kt * BK, a_bytes[a][j]);
-                }
+            if (tid == 0) {  // the stage is free: start this step's activation tiles
+                mbar_expect_tx(full_base + 8 * s, (uint32_t)(n_sub * TILE_BYTES));
+                for (int a = 0; a < n_sub; ++a)
+                    tma_load_a(stage_addr + a * TILE_BYTES, &x_map, kt * BK, tok0 + a * BM, full_base + 8 * s);
             }
 #pragma unroll
             for (int j = 0; j < SLOTS; ++j) {
@@ -227,7 +224,6 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
                                      pack_bf16x2(v2[4] * half_inv, v2[5] * half_inv), pack_bf16x2(v2[6] * half_inv, v2[7] * half_inv));
                 *reinterpret_cast<uint4*>(b_gen + slot_off[j]) = v;
             }
-            asm volatile("cp.async.wait_all;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
             __syncwarp();
             if (lane == 0) mbar_arrive(full_base + 8 * s);
@@ -258,25 +254,31 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
     ok = mbar_wait(done_bar, 0u) && ok;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    // epilogue: producer warp w reads TMEM lanes 32*(w%4).., columns 64*(w/4).. of every accumulator;
-    // one thread = one token row
+    // epilogue: producer warp w reads TMEM lanes 32*(w%4).., columns 64*(w/4).. of every accumulator
+    // (one thread = one token row, 32 consecutive features) and transposes each 32 x 32 piece through
+    // shared memory (the pipeline stages are idle by now), so that every global store instruction
+    // writes 128 contiguous bytes of one output row instead of 4 bytes of 32 different rows.
     if (warp < PRODUCERS / 32) {
         const int q = warp & 3, h = (warp >> 2) & 1;
+        float* scr = reinterpret_cast<float*>(gen) + warp * (32 * 33);  // 16 warps x 4.1 KiB inside stage 0
         for (int a = warp >> 3; a < n_sub; a += PRODUCERS / 256) {
-            const int tok = tok0 + a * BM + q * 32 + lane;
+            const int tok_first = tok0 + a * BM + q * 32;
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
                 uint32_t r[32];
                 const int col0 = h * 64 + cc * 32;
                 tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + col0), r);
-                if (tok < T && ok) {
-                    float* dst = y + (int64_t)tok * ldy + (int64_t)tile_n * BN + col0;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        int n = tile_n * BN + col0 + j;
-                        if (n < N) dst[j] = __uint_as_float(r[j]) + (bias ? __ldg(bias + n) : 0.0f);
-                    }
+                for (int j = 0; j < 32; ++j) scr[lane * 33 + j] = __uint_as_float(r[j]);
+                __syncwarp();
+                const int n = tile_n * BN + col0 + lane;
+                const float bv = (bias && n < N) ? __ldg(bias + n) : 0.0f;
+                if (ok && n < N) {
+                    float* dst = y + (int64_t)tok_first * ldy + n;
+                    const int rows = T - tok_first < 32 ? T - tok_first : 32;
+                    for (int rr = 0; rr < rows; ++rr) dst[(int64_t)rr * ldy] = scr[rr * 33 + lane] + bv;
                 }
+                __syncwarp();
             }
         }
     }
@@ -286,6 +288,32 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TMEM_COLS) : "memory");
     }
+}
+
+// Tensor map of the activations x[T, K] (bf16, row stride ldx): boxes of 64 (K) x 128 (rows), 128-byte
+// swizzle, zero fill outside the tensor.  The driver entry point is looked up through the runtime so
+// that the library does not link against the driver library.
+int make_x_map(CUtensorMap* map, const void* x, int K, int T, int64_t ldx) {
+    typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeTiled encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (check_cuda(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres), "cudaGetDriverEntryPoint")) return COSET_E_STATE;
+        if (qres != cudaDriverEntryPointSuccess || !fn) return fail(COSET_E_STATE, "cuTensorMapEncodeTiled is not available in this driver");
+        encode = (EncodeTiled)fn;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)T};
+    const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};  // bytes between rows; a multiple of 16 (ldx % 8 == 0)
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(COSET_E_BADARG, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
 }
 
 }  // namespace
@@ -298,6 +326,8 @@ extern "C" int coset_e8_dequant_gemm(const void* codes, const float* beta, int64
     if (!codes || !x_bf16 || !y) return fail(COSET_E_BADARG, "null pointer");
     if (ldx < n_in || ldy < n_out || (ldx % 8) != 0) return fail(COSET_E_BADARG, "leading dimensions: ldx >= n_in and a multiple of 8, ldy >= n_out");
     if (!aligned(x_bf16, 16) || !aligned(codes, 4)) return fail(COSET_E_ALIGN, "x must be 16-byte and codes 4-byte aligned");
+    CUtensorMap x_map;
+    if (int e = make_x_map(&x_map, x_bf16, n_in, T, ldx)) return e;
     if (beta && blocks_per_tile < 1) return fail(COSET_E_BADARG, "blocks_per_tile must be >= 1");
     cudaStream_t st = (cudaStream_t)stream;
     const uint2* table = residual_table_q4(st);
@@ -307,10 +337,10 @@ extern "C" int coset_e8_dequant_gemm(const void* codes, const float* beta, int64
     if (grid.y > 65535) return fail(COSET_E_UNSUPPORTED, "T too large");
     if (beta) {
         if (int e = check_cuda(cudaFuncSetAttribute(k_dequant_gemm<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), "cudaFuncSetAttribute")) return e;
-        k_dequant_gemm<2><<<grid, THREADS, SMEM_BYTES, st>>>((const uint32_t*)codes, beta, td, n_out, n_in, (const __nv_bfloat16*)x_bf16, ldx, T, bias, table, y, ldy, status);
+        k_dequant_gemm<2><<<grid, THREADS, SMEM_BYTES, st>>>((const uint32_t*)codes, beta, td, n_out, n_in, x_map, T, bias, table, y, ldy, status);
     } else {
         if (int e = check_cuda(cudaFuncSetAttribute(k_dequant_gemm<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), "cudaFuncSetAttribute")) return e;
-        k_dequant_gemm<0><<<grid, THREADS, SMEM_BYTES, st>>>((const uint32_t*)codes, beta, td, n_out, n_in, (const __nv_bfloat16*)x_bf16, ldx, T, bias, table, y, ldy, status);
+        k_dequant_gemm<0><<<grid, THREADS, SMEM_BYTES, st>>>((const uint32_t*)codes, beta, td, n_out, n_in, x_map, T, bias, table, y, ldy, status);
     }
     return check_launch("e8_dequant_gemm");
 }
