@@ -213,12 +213,22 @@ k_encode_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::T
 // with all lanes busy, each lane completing one queued block with the always-valid tiers.
 // In the regime where most blocks need the top level (an overloaded quantiser) the level is run
 // in place instead, so the queue only ever carries the rare cases.
-constexpr int kQueueSlots = 64;   // < 32 left after a drain + at most 32 new per step
+constexpr int kQueueSlots = 64;   // < 32 left after a drain + at most 32 new per sub-step
+constexpr int kRowsPerIter = 2;   // rows per lane and loop iteration
 constexpr int kEncWarps = kThreads / 32;
 
 // RECON = false: codes only (e8_encode).  RECON = true: the fused round trip -- every finished code is
 // decoded through the residual table, unscaled, clamped and written as [n, 8] of type DTO; the
 // packed code is stored only if `codes` is not null (e8_quantize / the layer's weight path).
+// CTAs of the queued encoder: enough for every warp to get one iteration, at most kEncCtasPerSm per SM.
+constexpr int kEncCtasPerSm = 12;
+inline unsigned encoder_grid(int64_t n_blocks) {
+    const int64_t per_cta = (int64_t)kThreads * kRowsPerIter;
+    const int64_t need = (n_blocks + per_cta - 1) / per_cta;
+    const int64_t cap = (int64_t)sm_count() * kEncCtasPerSm;
+    return (unsigned)(need < cap ? (need < 1 ? 1 : need) : cap);
+}
+
 template <int DT, int MODE, bool RECON, int DTO>
 __global__ void __launch_bounds__(kThreads, 4)
 k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
@@ -241,99 +251,140 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t lanes_below = (1u << lane) - 1u;
     int count = 0;  // warp-uniform number of queued blocks
-    int64_t base = ((int64_t)blockIdx.x * kEncWarps + warp) * 32;
-    const int64_t stride = (int64_t)gridDim.x * kThreads;
-    bool more = base < n;
-    while (true) {
-        if (more) {
-            const int64_t b = base + lane;
-            const bool active = b < n;
+
+    // Scaled row of block b (only called for b < n).
+    auto load_row = [&](int64_t b, float (&v)[8], float& s) {
+        e8::Row8<DT>::load(x, b, v);
+        s = load_scale<MODE>(scale, td, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = scale_in<MODE>(v[i], s);
+    };
+    // Completes up to 32 queued blocks with all lanes busy and moves the rest to the front.
+    auto drain = [&]() {
+        __syncwarp();
+        const int take = count < 32 ? count : 32;
+        if (lane < take) {
             float v[8];
-            float s = 1.0f;
-            if (active) {
-                e8::Row8<DT>::load(x, b, v);
-                s = load_scale<MODE>(scale, td, b);
-            } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = 0.0f;
-            }
-            float amax = 0.0f, s1 = 0.0f;
+            for (int i = 0; i < 8; ++i) v[i] = q_x[warp][i][lane];
+            uint32_t code = q_meta[warp][0][lane];
+            int64_t b = (int64_t)(((uint64_t)q_meta[warp][2][lane] << 32) | q_meta[warp][1][lane]);
+            int start = (int)q_meta[warp][3][lane];
+            float sc = __uint_as_float(q_meta[warp][4][lane]);
+            emit(b, e8::finish_block_q4(v, code, start), sc);
+        }
+        __syncwarp();
+        const int rem = count - take;
+        if (lane < rem) {  // move the tail (fewer than 32 entries) to the front
+            float t[8];
+            uint32_t u[5];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                v[i] = scale_in<MODE>(v[i], s);
-                amax = fmaxf(amax, fabsf(v[i]));
-                s1 += fabsf(v[i]);
-            }
-            const bool finite = (s1 - s1) == 0.0f;
-            uint32_t code = 0;
-            int open_level = 2;  // 2 = finished
-            if (!finite) {
-                open_level = 0;
-            } else if (!(amax <= 0.49f && s1 <= 1.99f)) {
-                if (!e8::level_fast_q4<false>(v, amax, code)) open_level = 0;
-            }
-            // top level: origin unless max|x| > 1.96 or sum|x| > 7.96 (the level sees x / 4)
-            bool need1 = active && open_level == 2 && !(amax <= 1.96f && s1 <= 7.96f);
-            if (__popc(__ballot_sync(0xffffffffu, need1)) >= 12) {
-                if (need1) {
-                    float v1[8];
+            for (int i = 0; i < 8; ++i) t[i] = q_x[warp][i][32 + lane];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) v1[i] = __fmul_rn(v[i], 0.25f);
-                    uint32_t d1;
-                    if (e8::level_fast_q4<false>(v1, amax * 0.25f, d1)) code |= d1 << 16; else open_level = 1;
+            for (int i = 0; i < 5; ++i) u[i] = q_meta[warp][i][32 + lane];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) q_x[warp][i][lane] = t[i];
+#pragma unroll
+            for (int i = 0; i < 5; ++i) q_meta[warp][i][lane] = u[i];
+        }
+        __syncwarp();
+        count = rem;
+    };
+
+    // One loop iteration of a warp covers kRowsPerIter * 32 consecutive blocks, one row per lane and
+    // sub-step.  All rows are requested first; the cheap level-0 path then runs row after row in
+    // straight-line code, which lets the loads of later rows and the FP32-heavy head of one row
+    // overlap the ALU-heavy tail of the previous one.  The rows are not kept: the rare lane that
+    // has to defer its block (or run the top level in place) reads its row again (an L1/L2 hit).
+    const int64_t span = 32 * kRowsPerIter;
+    const int64_t stride = (int64_t)gridDim.x * kEncWarps * span;
+    for (int64_t base = ((int64_t)blockIdx.x * kEncWarps + warp) * span; base < n; base += stride) {
+        uint32_t code[kRowsPerIter];
+        int open_level[kRowsPerIter];  // 2 = finished, else the first level still open
+        bool need1[kRowsPerIter];
+        float sc[kRowsPerIter];
+        {
+            float v[kRowsPerIter][8];
+#pragma unroll
+            for (int j = 0; j < kRowsPerIter; ++j) {
+                const int64_t b = base + j * 32 + lane;
+                sc[j] = 1.0f;
+                if (b < n) {
+                    e8::Row8<DT>::load(x, b, v[j]);
+                    sc[j] = load_scale<MODE>(scale, td, b);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[j][i] = 0.0f;
                 }
-            } else if (need1) {
-                open_level = 1;
             }
-            const bool defer = active && open_level != 2;
+#pragma unroll
+            for (int j = 0; j < kRowsPerIter; ++j) {
+                const bool active = base + j * 32 + lane < n;
+                float s1 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    v[j][i] = scale_in<MODE>(v[j][i], sc[j]);
+                    s1 += fabsf(v[j][i]);
+                }
+                // max |x_i| as a tree of three-input maxima (4 instructions instead of 8)
+                const float m0 = fmaxf(fmaxf(fabsf(v[j][0]), fabsf(v[j][1])), fabsf(v[j][2]));
+                const float m1 = fmaxf(fmaxf(fabsf(v[j][3]), fabsf(v[j][4])), fabsf(v[j][5]));
+                const float amax = fmaxf(fmaxf(m0, m1), fmaxf(fabsf(v[j][6]), fabsf(v[j][7])));
+                const bool finite = (s1 - s1) == 0.0f;
+                code[j] = 0;
+                open_level[j] = 2;
+                if (!finite) {
+                    open_level[j] = 0;
+                } else if (!(amax <= 0.49f && s1 <= 1.99f)) {
+                    if (!e8::level_fast_q4<false>(v[j], amax, code[j])) open_level[j] = 0;
+                }
+                // top level: origin unless max|x| > 1.96 or sum|x| > 7.96 (the level sees x / 4)
+                need1[j] = active && open_level[j] == 2 && !(amax <= 1.96f && s1 <= 7.96f);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kRowsPerIter; ++j) {
+            const int64_t b = base + j * 32 + lane;
+            const bool active = b < n;
+            const uint32_t bal1 = __ballot_sync(0xffffffffu, need1[j]);
+            if (bal1 != 0u && __popc(bal1) >= 12) {
+                if (need1[j]) {  // an overloaded quantiser: most lanes need the top level, run it in place
+                    float v[8], v1[8], s;
+                    load_row(b, v, s);
+                    float amax = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        v1[i] = __fmul_rn(v[i], 0.25f);
+                        amax = fmaxf(amax, fabsf(v1[i]));
+                    }
+                    uint32_t d1;
+                    if (e8::level_fast_q4<false>(v1, amax, d1)) code[j] |= d1 << 16; else open_level[j] = 1;
+                }
+            } else if (need1[j]) {
+                open_level[j] = 1;
+            }
+            const bool defer = active && open_level[j] != 2;
             const uint32_t bal = __ballot_sync(0xffffffffu, defer);
-            if (active && !defer) emit(b, code, s);
-            if (defer) {
-                const int pos = count + __popc(bal & lanes_below);
+            if (active && !defer) emit(b, code[j], sc[j]);
+            if (bal) {
+                if (defer) {
+                    float v[8], s;
+                    load_row(b, v, s);
+                    const int pos = count + __popc(bal & lanes_below);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) q_x[warp][i][pos] = v[i];
-                q_meta[warp][0][pos] = code;
-                q_meta[warp][1][pos] = (uint32_t)b;
-                q_meta[warp][2][pos] = (uint32_t)((uint64_t)b >> 32);
-                q_meta[warp][3][pos] = (uint32_t)open_level;
-                q_meta[warp][4][pos] = __float_as_uint(s);
+                    for (int i = 0; i < 8; ++i) q_x[warp][i][pos] = v[i];
+                    q_meta[warp][0][pos] = code[j];
+                    q_meta[warp][1][pos] = (uint32_t)b;
+                    q_meta[warp][2][pos] = (uint32_t)((uint64_t)b >> 32);
+                    q_meta[warp][3][pos] = (uint32_t)open_level[j];
+                    q_meta[warp][4][pos] = __float_as_uint(s);
+                }
+                count += __popc(bal);
+                if (count >= 32) drain();
             }
-            count += __popc(bal);
-            base += stride;
-            more = base < n;
         }
-        if (count >= 32 || (!more && count > 0)) {
-            __syncwarp();
-            const int take = count < 32 ? count : 32;
-            if (lane < take) {
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = q_x[warp][i][lane];
-                uint32_t code = q_meta[warp][0][lane];
-                int64_t b = (int64_t)(((uint64_t)q_meta[warp][2][lane] << 32) | q_meta[warp][1][lane]);
-                int start = (int)q_meta[warp][3][lane];
-                float sc = __uint_as_float(q_meta[warp][4][lane]);
-                emit(b, e8::finish_block_q4(v, code, start), sc);
-            }
-            __syncwarp();
-            const int rem = count - take;
-            if (lane < rem) {  // move the tail (fewer than 32 entries) to the front
-                float t[8];
-                uint32_t u[5];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) t[i] = q_x[warp][i][32 + lane];
-#pragma unroll
-                for (int i = 0; i < 5; ++i) u[i] = q_meta[warp][i][32 + lane];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) q_x[warp][i][lane] = t[i];
-#pragma unroll
-                for (int i = 0; i < 5; ++i) q_meta[warp][i][lane] = u[i];
-            }
-            __syncwarp();
-            count = rem;
-        }
-        if (!more && count == 0) break;
     }
+    while (count > 0) drain();
 }
 
 // Two blocks per thread (kThreads apart, so every access stays coalesced): both codes are
@@ -530,7 +581,7 @@ int coset_e8_encode(const void* x, int x_dtype, const float* scale, int scale_mo
     unsigned grid = grid_for(n_blocks);
     if (q == 4 && M == 2 && sem == COSET_SEM_CORE) {
         // persistent warps: 16 CTAs per SM worth of grid (4 resident at a time) balances queue fill and tail
-        unsigned qgrid = grid < (unsigned)(sm_count() * 16) ? grid : (unsigned)(sm_count() * 16);
+        unsigned qgrid = encoder_grid(n_blocks);
         DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2_queued<DT, MODE, false, 0><<<qgrid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes, nullptr, nullptr, 0.0f))))
     } else if (q == 4 && M == 2) {
         DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2<DT, MODE, true><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes))))
@@ -585,7 +636,7 @@ int coset_e8_quantize(const void* x, int x_dtype, const float* scale, int scale_
     if (q == 4 && M == 2) {
         const uint2* table = residual_table_q4(st);
         if (!table) return COSET_E_STATE;
-        unsigned qgrid = grid < (unsigned)(sm_count() * 16) ? grid : (unsigned)(sm_count() * 16);
+        unsigned qgrid = encoder_grid(n_blocks);
         DISPATCH_DT(x_dtype, DTI, DISPATCH_DT(out_dtype, DTO, DISPATCH_MODE(scale_mode, (k_encode_q4m2_queued<DTI, MODE, true, DTO><<<qgrid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes_out, table, out, clip)))))
     } else if (q <= 4) {
         DISPATCH_DT(x_dtype, DTI, DISPATCH_DT(out_dtype, DTO, DISPATCH_MODE(scale_mode, (k_quantize_generic<DTI, DTO, MODE, 2><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, q, M, clip, out, codes_out)))))
