@@ -205,21 +205,21 @@ k_encode_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::T
 
 // Queued encoder (the production path for q=4, M=2).
 //
-// Warps are persistent and take 32 consecutive blocks per step.  Every lane runs the cheap
-// rint-based level-0 path; whatever that path cannot finish -- a block on a rounding tie, a block
-// whose top level is not the origin, a non-finite block -- is NOT handled in place (that would
-// idle the other 31 lanes for hundreds of instructions) but appended to a per-warp queue in shared
-// memory.  When 32 entries have accumulated (and once at the end) the warp drains the queue
-// with all lanes busy, each lane completing one queued block with the always-valid tiers.
-// In the regime where most blocks need the top level (an overloaded quantiser) the level is run
-// in place instead, so the queue only ever carries the rare cases.
-constexpr int kQueueSlots = 64;   // < 32 left after a drain + at most 32 new per sub-step
+// Warps are persistent; one loop iteration of a warp covers kRowsPerIter * 32 consecutive blocks,
+// one row per lane and sub-step.  Every lane runs the cheap rint-based level-0 path; whatever that
+// path cannot finish -- a block on a rounding tie, a block whose top level is not the origin, a
+// non-finite block -- is NOT handled in place (that would idle the other 31 lanes for hundreds of
+// instructions): the lane appends the block's index, its code so far and its first open level to
+// a per-warp queue in shared memory (a shared-memory atomic hands out the slot, so no warp-wide
+// vote sits on the common path).  Once per iteration the warp looks at the queue length; with 32
+// or more entries (and at the end) it drains 32 of them with all lanes busy: every lane reads the
+// row of its entry again -- one memory round trip per 32 deferred blocks -- and completes it with
+// the always-valid tiers.  When the previous iteration deferred most of its blocks because of the
+// top level (an overloaded quantiser) that level is run in place instead.
 constexpr int kRowsPerIter = 2;   // rows per lane and loop iteration
+constexpr int kQueueSlots = 32 * (kRowsPerIter + 1);  // < 32 left after a drain + at most 32 per sub-step
 constexpr int kEncWarps = kThreads / 32;
 
-// RECON = false: codes only (e8_encode).  RECON = true: the fused round trip -- every finished code is
-// decoded through the residual table, unscaled, clamped and written as [n, 8] of type DTO; the
-// packed code is stored only if `codes` is not null (e8_quantize / the layer's weight path).
 // CTAs of the queued encoder: enough for every warp to get one iteration, at most kEncCtasPerSm per SM.
 constexpr int kEncCtasPerSm = 12;
 inline unsigned encoder_grid(int64_t n_blocks) {
@@ -229,12 +229,15 @@ inline unsigned encoder_grid(int64_t n_blocks) {
     return (unsigned)(need < cap ? (need < 1 ? 1 : need) : cap);
 }
 
+// RECON = false: codes only (e8_encode).  RECON = true: the fused round trip -- every finished code is
+// decoded through the residual table, unscaled, clamped and written as [n, 8] of type DTO; the
+// packed code is stored only if `codes` is not null (e8_quantize / the layer's weight path).
 template <int DT, int MODE, bool RECON, int DTO>
 __global__ void __launch_bounds__(kThreads, 4)
 k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
                      uint32_t* __restrict__ codes, const uint2* __restrict__ table, void* __restrict__ out, float clip) {
-    __shared__ float q_x[kEncWarps][8][kQueueSlots];
-    __shared__ uint32_t q_meta[kEncWarps][5][kQueueSlots];  // code so far, block index lo / hi, first open level, scale
+    __shared__ uint32_t q_meta[kEncWarps][4][kQueueSlots];  // block index lo / hi, code so far, first open level
+    __shared__ int q_count[kEncWarps];
     auto emit = [&](int64_t b, uint32_t code, float s) {
         if (!RECON) {
             __stcs(codes + b, code);
@@ -249,8 +252,9 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
         }
     };
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t lanes_below = (1u << lane) - 1u;
-    int count = 0;  // warp-uniform number of queued blocks
+    if (lane == 0) q_count[warp] = 0;
+    __syncwarp();
+    int count = 0;  // warp-uniform copy of q_count[warp] as of the last look
 
     // Scaled row of block b (only called for b < n).
     auto load_row = [&](int64_t b, float (&v)[8], float& s) {
@@ -259,51 +263,36 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = scale_in<MODE>(v[i], s);
     };
-    // Completes up to 32 queued blocks with all lanes busy and moves the rest to the front.
+    // Completes the last min(count, 32) queued blocks with all lanes busy.
     auto drain = [&]() {
-        __syncwarp();
         const int take = count < 32 ? count : 32;
         if (lane < take) {
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = q_x[warp][i][lane];
-            uint32_t code = q_meta[warp][0][lane];
-            int64_t b = (int64_t)(((uint64_t)q_meta[warp][2][lane] << 32) | q_meta[warp][1][lane]);
-            int start = (int)q_meta[warp][3][lane];
-            float sc = __uint_as_float(q_meta[warp][4][lane]);
-            emit(b, e8::finish_block_q4(v, code, start), sc);
+            const int e = count - take + lane;
+            const int64_t b = (int64_t)(((uint64_t)q_meta[warp][1][e] << 32) | q_meta[warp][0][e]);
+            const uint32_t code = q_meta[warp][2][e];
+            const int start = (int)q_meta[warp][3][e];
+            float v[8], s;
+            load_row(b, v, s);
+            emit(b, e8::finish_block_q4(v, code, start), s);
         }
+        count -= take;
         __syncwarp();
-        const int rem = count - take;
-        if (lane < rem) {  // move the tail (fewer than 32 entries) to the front
-            float t[8];
-            uint32_t u[5];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) t[i] = q_x[warp][i][32 + lane];
-#pragma unroll
-            for (int i = 0; i < 5; ++i) u[i] = q_meta[warp][i][32 + lane];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) q_x[warp][i][lane] = t[i];
-#pragma unroll
-            for (int i = 0; i < 5; ++i) q_meta[warp][i][lane] = u[i];
-        }
+        if (lane == 0) q_count[warp] = count;
         __syncwarp();
-        count = rem;
     };
 
-    // One loop iteration of a warp covers kRowsPerIter * 32 consecutive blocks, one row per lane and
-    // sub-step.  All rows are requested first; the cheap level-0 path then runs row after row in
-    // straight-line code, which lets the loads of later rows and the FP32-heavy head of one row
-    // overlap the ALU-heavy tail of the previous one.  The rows are not kept: the rare lane that
-    // has to defer its block (or run the top level in place) reads its row again (an L1/L2 hit).
     const int64_t span = 32 * kRowsPerIter;
     const int64_t stride = (int64_t)gridDim.x * kEncWarps * span;
+    bool hot = false;  // the previous iteration deferred most of its blocks
     for (int64_t base = ((int64_t)blockIdx.x * kEncWarps + warp) * span; base < n; base += stride) {
         uint32_t code[kRowsPerIter];
         int open_level[kRowsPerIter];  // 2 = finished, else the first level still open
         bool need1[kRowsPerIter];
         float sc[kRowsPerIter];
         {
+            // All rows are requested first; the level-0 path then runs row after row in straight-line
+            // code, so the loads of the later rows and the FP32-heavy head of one row overlap the
+            // ALU-heavy tail of the previous one.  The rows are not kept beyond this scope.
             float v[kRowsPerIter][8];
 #pragma unroll
             for (int j = 0; j < kRowsPerIter; ++j) {
@@ -346,9 +335,9 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
         for (int j = 0; j < kRowsPerIter; ++j) {
             const int64_t b = base + j * 32 + lane;
             const bool active = b < n;
-            const uint32_t bal1 = __ballot_sync(0xffffffffu, need1[j]);
-            if (bal1 != 0u && __popc(bal1) >= 12) {
-                if (need1[j]) {  // an overloaded quantiser: most lanes need the top level, run it in place
+            if (need1[j]) {
+                open_level[j] = 1;
+                if (hot) {  // overloaded quantiser: most lanes are here, so the top level runs in place
                     float v[8], v1[8], s;
                     load_row(b, v, s);
                     float amax = 0.0f;
@@ -358,31 +347,29 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
                         amax = fmaxf(amax, fabsf(v1[i]));
                     }
                     uint32_t d1;
-                    if (e8::level_fast_q4<false>(v1, amax, d1)) code[j] |= d1 << 16; else open_level[j] = 1;
+                    if (e8::level_fast_q4<false>(v1, amax, d1)) {
+                        code[j] |= d1 << 16;
+                        open_level[j] = 2;
+                    }
                 }
-            } else if (need1[j]) {
-                open_level[j] = 1;
             }
-            const bool defer = active && open_level[j] != 2;
-            const uint32_t bal = __ballot_sync(0xffffffffu, defer);
-            if (active && !defer) emit(b, code[j], sc[j]);
-            if (bal) {
-                if (defer) {
-                    float v[8], s;
-                    load_row(b, v, s);
-                    const int pos = count + __popc(bal & lanes_below);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) q_x[warp][i][pos] = v[i];
-                    q_meta[warp][0][pos] = code[j];
-                    q_meta[warp][1][pos] = (uint32_t)b;
-                    q_meta[warp][2][pos] = (uint32_t)((uint64_t)b >> 32);
+            if (active) {
+                if (open_level[j] == 2) {
+                    emit(b, code[j], sc[j]);
+                } else {
+                    const int pos = atomicAdd(&q_count[warp], 1);
+                    q_meta[warp][0][pos] = (uint32_t)b;
+                    q_meta[warp][1][pos] = (uint32_t)((uint64_t)b >> 32);
+                    q_meta[warp][2][pos] = code[j];
                     q_meta[warp][3][pos] = (uint32_t)open_level[j];
-                    q_meta[warp][4][pos] = __float_as_uint(s);
                 }
-                count += __popc(bal);
-                if (count >= 32) drain();
             }
         }
+        __syncwarp();
+        const int now = *reinterpret_cast<volatile int*>(&q_count[warp]);
+        hot = (now - count) >= 12 * kRowsPerIter;
+        count = now;
+        while (count >= 32) drain();
     }
     while (count > 0) drain();
 }
