@@ -216,7 +216,7 @@ k_encode_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::T
 // row of its entry again -- one memory round trip per 32 deferred blocks -- and completes it with
 // the always-valid tiers.  When the previous iteration deferred most of its blocks because of the
 // top level (an overloaded quantiser) that level is run in place instead.
-constexpr int kRowsPerIter = 2;   // rows per lane and loop iteration
+constexpr int kRowsPerIter = 3;   // rows per lane and loop iteration (measured: 1 -> 0.464 ms, 2 -> 0.425, 3 -> 0.415, 4 -> 0.431)
 constexpr int kQueueSlots = 32 * (kRowsPerIter + 1);  // < 32 left after a drain + at most 32 per sub-step
 constexpr int kEncWarps = kThreads / 32;
 
