@@ -39,7 +39,7 @@ BETA_LITERAL = 0.021440971642732620
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one encode launch, from the ncu capture
 # summarised in profiles/, scaled to the full launch by the number of blocks.
-ENCODE_TRAFFIC_BYTES_PER_LAUNCH = 1.2725e9  # 8 x (151.03 + 8.03) MB: dram read + write of one ncu capture on 2^22 blocks, scaled to 2^25
+ENCODE_TRAFFIC_BYTES_PER_LAUNCH = 1.2723e9  # 8 x (151.12 + 7.92) MB: dram read + write of one ncu capture on 2^22 blocks, scaled to 2^25
 
 
 def make_values(n_values, seed):
