@@ -214,8 +214,9 @@ k_encode_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::T
 // vote sits on the common path).  Once per iteration the warp looks at the queue length; with 32
 // or more entries (and at the end) it drains 32 of them with all lanes busy: every lane reads the
 // row of its entry again -- one memory round trip per 32 deferred blocks -- and completes it with
-// the always-valid tiers.  When the previous iteration deferred most of its blocks because of the
-// top level (an overloaded quantiser) that level is run in place instead.
+// the always-valid tiers.  This also serves an overloaded quantiser, where most blocks need the top
+// level: the queue then fills every iteration and is drained by full warps (running that level in
+// place for the lanes that need it was measured and is slower at every scale).
 constexpr int kRowsPerIter = 3;   // rows per lane and loop iteration (measured: 1 -> 0.464 ms, 2 -> 0.425, 3 -> 0.415, 4 -> 0.431)
 constexpr int kQueueSlots = 32 * (kRowsPerIter + 1);  // < 32 left after a drain + at most 32 per sub-step
 constexpr int kEncWarps = kThreads / 32;
@@ -283,7 +284,6 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
 
     const int64_t span = 32 * kRowsPerIter;
     const int64_t stride = (int64_t)gridDim.x * kEncWarps * span;
-    bool hot = false;  // the previous iteration deferred most of its blocks
     for (int64_t base = ((int64_t)blockIdx.x * kEncWarps + warp) * span; base < n; base += stride) {
         uint32_t code[kRowsPerIter];
         int open_level[kRowsPerIter];  // 2 = finished, else the first level still open
@@ -335,24 +335,7 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
         for (int j = 0; j < kRowsPerIter; ++j) {
             const int64_t b = base + j * 32 + lane;
             const bool active = b < n;
-            if (need1[j]) {
-                open_level[j] = 1;
-                if (hot) {  // overloaded quantiser: most lanes are here, so the top level runs in place
-                    float v[8], v1[8], s;
-                    load_row(b, v, s);
-                    float amax = 0.0f;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        v1[i] = __fmul_rn(v[i], 0.25f);
-                        amax = fmaxf(amax, fabsf(v1[i]));
-                    }
-                    uint32_t d1;
-                    if (e8::level_fast_q4<false>(v1, amax, d1)) {
-                        code[j] |= d1 << 16;
-                        open_level[j] = 2;
-                    }
-                }
-            }
+            if (need1[j]) open_level[j] = 1;
             if (active) {
                 if (open_level[j] == 2) {
                     emit(b, code[j], sc[j]);
@@ -366,9 +349,7 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
             }
         }
         __syncwarp();
-        const int now = *reinterpret_cast<volatile int*>(&q_count[warp]);
-        hot = (now - count) >= 12 * kRowsPerIter;
-        count = now;
+        count = *reinterpret_cast<volatile int*>(&q_count[warp]);
         while (count >= 32) drain();
     }
     while (count > 0) drain();
