@@ -69,6 +69,25 @@ def graph_time(fn, calls=20, replays=10):
     return a.elapsed_time(b) / (calls * replays)
 
 
+def graph_step_time(layer, x, t):
+    """Forward + backward of the layer captured once into a CUDA graph and replayed (the layer's kernels
+    only enqueue work on the current stream, so the whole step is capturable; the 1-in-256 statistics
+    update is a host-side branch and is not part of the captured step)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            layer.zero_grad(set_to_none=True)
+            ((layer(x) - t).float() ** 2).mean().backward()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    layer.zero_grad(set_to_none=True)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        ((layer(x) - t).float() ** 2).mean().backward()
+    return cuda_time(lambda: g.replay())
+
+
 def bench_qat():
     from .core.e8 import create_e8_hnlq_linear
     from .core.layers import e8_fake_quantize
@@ -87,6 +106,7 @@ def bench_qat():
                 ((y - t).float() ** 2).mean().backward()
 
             ms = cuda_time(step)
+            ms_graph = graph_step_time(layer, x, t)
             beta = layer._beta().detach()
             bpt = layer.blocks_per_row if tiling == "row" else 1
             w = layer.weight.detach()
@@ -96,6 +116,8 @@ def bench_qat():
             print(json.dumps({
                 "bench": "qat_step", "weights": tag, "tiling": tiling, "tokens": tokens, "shape": [d_out, d_in],
                 "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3),
+                "graph_ms_per_step": ms_graph, "graph_tokens_per_s": tokens / (ms_graph * 1e-3),
+                "note": "eager steps are bound by the Python / launch path; the graph replays the same forward + backward",
                 "gemm_tflops_equiv": 3 * 2 * tokens * d_in * d_out / (ms * 1e-3) / 1e12,
                 "fake_quant_fwd_ms": fq, "fake_quant_fwd_GBps": fq_bytes / (fq * 1e-3) / 1e9,
                 "fake_quant_frac_of_hbm": fq_bytes / (fq * 1e-3) / 1e9 / hbm, "peaks": src}), flush=True)

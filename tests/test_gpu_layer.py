@@ -121,3 +121,40 @@ def test_bf16_activations(golden_layer):
     assert rel(y16.detach().float().cpu().numpy(), y32.detach().cpu().numpy()) < 1e-2
     y16.float().sum().backward()
     assert layer.weight.grad is not None and layer.theta_beta.grad is not None
+
+
+def test_training_step_is_graph_capturable():
+    """Forward + backward of the layer enqueue work only on the current stream: one CUDA graph replays
+    the step and yields the gradients of the eager step."""
+    import warnings
+    from coset_b200.core.e8 import create_e8_hnlq_linear
+    torch.manual_seed(0)
+    layer = create_e8_hnlq_linear(64, 48, q=4, M=2, init_kwargs={"std": 20.0}, device="cuda")
+    x = torch.randn(32, 64, device="cuda")
+    t = torch.randn(32, 48, device="cuda")
+
+    def step():
+        ((layer(x) - t) ** 2).mean().backward()
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            layer.zero_grad(set_to_none=True)
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    layer.zero_grad(set_to_none=True)
+    g = torch.cuda.CUDAGraph()
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        with torch.cuda.graph(g):
+            step()
+    g.replay()
+    torch.cuda.synchronize()
+    gw, gt = layer.weight.grad.clone(), layer.theta_beta.grad.clone()
+    layer.zero_grad(set_to_none=True)
+    step()
+    torch.cuda.synchronize()
+    assert torch.equal(gw, layer.weight.grad)
+    assert torch.allclose(gt, layer.theta_beta.grad, rtol=1e-6, atol=0)
