@@ -299,6 +299,21 @@ def main():
                "api": "coset_b200.host.HostCodec.encode/.decode -> coset_e8_encode_host / coset_e8_decode_host"}
         ok = torch.equal(oh[:4096], xhat[:4096].cpu())
         e2e["matches_device_path"] = bool(ok)
+        # the same host arrays through the one-pass round trip (codes and reconstruction both returned;
+        # the codes are not uploaded again, so both PCIe directions are busy at once)
+        oh2 = torch.empty((n, 8), dtype=torch.float32, pin_memory=True)
+        hc.quantize(xh, scale=bh, scale_mode=MT, out=oh2, codes_out=ch)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            hc.quantize(xh, scale=bh, scale_mode=MT, out=oh2, codes_out=ch)
+        torch.cuda.synchronize()
+        dt2 = time.perf_counter() - t0
+        e2e["one_pass_roundtrip"] = {"value": e2e_steps * n * BYTES_PER_BLOCK_STEP / dt2 / 1e9, "unit": "GB/s (this rank)",
+                                     "h2d_bytes_per_step": n * (32 + 4), "d2h_bytes_per_step": n * (32 + 4),
+                                     "api": "HostCodec.quantize -> coset_e8_quantize_host",
+                                     "matches_two_call_path": bool(torch.equal(oh2[:4096], oh[:4096]))}
+        del oh2
         hc.close()
         del xh, ch, oh
 

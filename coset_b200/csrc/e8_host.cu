@@ -20,6 +20,7 @@ struct coset_host_ctx {
         void* x;       // chunk_blocks * 32 B  (float32 rows; bf16 uses half)
         void* codes;   // chunk_blocks * 32 B  (largest packed code: M=8, 4 B per level)
         float* scale;  // chunk_blocks * 4 B
+        void* recon;   // chunk_blocks * 32 B, allocated by the first round-trip call
     } slots[8];
 };
 
@@ -31,6 +32,7 @@ void destroy(coset_host_ctx* c) {
         if (c->slots[i].x) cudaFree(c->slots[i].x);
         if (c->slots[i].codes) cudaFree(c->slots[i].codes);
         if (c->slots[i].scale) cudaFree(c->slots[i].scale);
+        if (c->slots[i].recon) cudaFree(c->slots[i].recon);
         if (c->slots[i].stream) cudaStreamDestroy(c->slots[i].stream);
     }
     delete c;
@@ -67,7 +69,7 @@ int coset_host_ctx_create(int64_t chunk_blocks, int n_slots, coset_host_ctx** ou
     if (int e = check_cuda(cudaGetDevice(&c->device), "cudaGetDevice")) { delete c; return e; }
     for (int i = 0; i < n_slots; ++i) {
         coset_host_ctx::Slot& s = c->slots[i];
-        s = {nullptr, nullptr, nullptr, nullptr};
+        s = {nullptr, nullptr, nullptr, nullptr, nullptr};
         c->n_slots = i + 1;
         cudaError_t e = cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking);
         if (e == cudaSuccess) e = cudaMalloc(&s.x, (size_t)chunk_blocks * 32);
@@ -150,6 +152,50 @@ int coset_e8_decode_host(coset_host_ctx* ctx, const void* codes_host, const floa
         rc = coset_e8_decode(s.codes, s.scale, scale_mode, nb, blocks_per_tile, q, M, COSET_SEM_CORE, s.x, out_dtype, s.stream);
         if (rc) break;
         rc = check_cuda(cudaMemcpyAsync((char*)out_host + lo * row, s.x, nb * row, cudaMemcpyDeviceToHost, s.stream), "D2H out");
+    }
+    int rs = sync_all(ctx);
+    return rc ? rc : rs;
+}
+
+int coset_e8_quantize_host(coset_host_ctx* ctx, const void* x_host, int x_dtype, const float* scale_host, int scale_mode,
+                           int64_t n_blocks, int64_t blocks_per_tile, int q, int M, float clip, void* out_host, int out_dtype,
+                           void* codes_host) {
+    if (!ctx) return fail(COSET_E_BADARG, "ctx is null");
+    if (n_blocks < 0 || (n_blocks > 0 && (!x_host || !out_host))) return fail(COSET_E_BADARG, "bad n_blocks or null buffer");
+    int cb = coset_e8_code_bytes(q, M);
+    if (!cb) return fail(COSET_E_UNSUPPORTED, "unsupported q=%d M=%d", q, M);
+    if ((x_dtype != COSET_DTYPE_F32 && x_dtype != COSET_DTYPE_BF16) || (out_dtype != COSET_DTYPE_F32 && out_dtype != COSET_DTYPE_BF16))
+        return fail(COSET_E_BADARG, "unknown dtype");
+    if (scale_mode != COSET_SCALE_NONE && !scale_host) return fail(COSET_E_BADARG, "scale_host is null");
+    if (scale_mode == COSET_SCALE_MUL_TILE && blocks_per_tile < 1) return fail(COSET_E_BADARG, "blocks_per_tile < 1");
+    int64_t chunk = chunk_for(ctx, scale_mode, blocks_per_tile);
+    if (chunk < 1) return fail(COSET_E_UNSUPPORTED, "blocks_per_tile exceeds the context's chunk size");
+    for (int i = 0; i < ctx->n_slots; ++i) {
+        if (!ctx->slots[i].recon) {
+            if (int e = check_cuda(cudaMalloc(&ctx->slots[i].recon, (size_t)ctx->chunk_blocks * 32), "cudaMalloc(round-trip staging)")) return e;
+        }
+    }
+    const size_t row_in = x_dtype == COSET_DTYPE_F32 ? 32 : 16, row_out = out_dtype == COSET_DTYPE_F32 ? 32 : 16;
+    int rc = 0, k = 0;
+    for (int64_t lo = 0; lo < n_blocks && !rc; lo += chunk, ++k) {
+        int64_t nb = n_blocks - lo < chunk ? n_blocks - lo : chunk;
+        coset_host_ctx::Slot& s = ctx->slots[k % ctx->n_slots];
+        rc = check_cuda(cudaMemcpyAsync(s.x, (const char*)x_host + lo * row_in, nb * row_in, cudaMemcpyHostToDevice, s.stream), "H2D x");
+        if (rc) break;
+        if (scale_mode == COSET_SCALE_DIV_SCALAR) {
+            rc = check_cuda(cudaMemcpyAsync(s.scale, scale_host, 4, cudaMemcpyHostToDevice, s.stream), "H2D scale");
+        } else if (scale_mode == COSET_SCALE_MUL_TILE) {
+            int64_t t0 = lo / blocks_per_tile, t1 = (lo + nb + blocks_per_tile - 1) / blocks_per_tile;
+            rc = check_cuda(cudaMemcpyAsync(s.scale, scale_host + t0, (t1 - t0) * 4, cudaMemcpyHostToDevice, s.stream), "H2D scale");
+        }
+        if (rc) break;
+        rc = coset_e8_quantize(s.x, x_dtype, s.scale, scale_mode, nb, blocks_per_tile, q, M, clip, s.recon, out_dtype,
+                               codes_host ? s.codes : nullptr, s.stream);
+        if (rc) break;
+        rc = check_cuda(cudaMemcpyAsync((char*)out_host + lo * row_out, s.recon, nb * row_out, cudaMemcpyDeviceToHost, s.stream), "D2H out");
+        if (rc) break;
+        if (codes_host)
+            rc = check_cuda(cudaMemcpyAsync((char*)codes_host + lo * cb, s.codes, nb * cb, cudaMemcpyDeviceToHost, s.stream), "D2H codes");
     }
     int rs = sync_all(ctx);
     return rc ? rc : rs;

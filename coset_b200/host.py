@@ -62,3 +62,23 @@ class HostCodec:
                                                  blocks_per_tile, q, M, self._host(out, "out"), _lib.dtype_code(out, "out"))
         _lib.check(rc, "coset_e8_decode_host")
         return out
+
+    def quantize(self, x, scale=None, scale_mode=_lib.SCALE_NONE, blocks_per_tile=1, q=4, M=2, clip=0.0,
+                 dtype=torch.float32, out=None, codes_out=None, return_codes=False):
+        """Round trip decode(encode(x)) in one pass over the host array: the input goes to the device while
+        the reconstructions (and the packed codes, if asked for) of earlier chunks come back.
+        -> CPU [N, 8] reconstruction, or (reconstruction, codes) with return_codes / codes_out."""
+        n = x.shape[0]
+        cb = _lib.lib().coset_e8_code_bytes(q, M)
+        if out is None:
+            out = torch.empty((n, 8), dtype=dtype, pin_memory=True)
+        if return_codes and codes_out is None:
+            codes_out = torch.empty((n, cb), dtype=torch.uint8, pin_memory=True)
+        sp = self._host(scale, "scale") if scale is not None else None
+        cp = self._host(codes_out, "codes_out") if codes_out is not None else None
+        with torch.cuda.device(self.device):
+            rc = _lib.lib().coset_e8_quantize_host(self._ctx, self._host(x, "x"), _lib.dtype_code(x, "x"), sp, scale_mode, n,
+                                                   blocks_per_tile, q, M, float(clip), self._host(out, "out"),
+                                                   _lib.dtype_code(out, "out"), cp)
+        _lib.check(rc, "coset_e8_quantize_host")
+        return (out, codes_out) if codes_out is not None else out

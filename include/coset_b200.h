@@ -148,6 +148,15 @@ int coset_e8_encode_host(coset_host_ctx* ctx, const void* x_host, int x_dtype, c
 int coset_e8_decode_host(coset_host_ctx* ctx, const void* codes_host, const float* scale_host,
                          int scale_mode, int64_t n_blocks, int64_t blocks_per_tile, int q, int M,
                          void* out_host, int out_dtype);
+/*
+ * Round trip over host arrays in one pass: coset_e8_quantize per chunk, so the input travels host ->
+ * device while reconstructions (and, if codes_host is not NULL, the packed codes) of earlier chunks
+ * travel back -- both PCIe directions are busy at once.  e8_quantize / decode(encode(x)) of
+ * coset/core/e8/codecs.py:221-286 for a CPU-side caller.  Holds n_slots * chunk_blocks * 32 B more.
+ */
+int coset_e8_quantize_host(coset_host_ctx* ctx, const void* x_host, int x_dtype, const float* scale_host,
+                           int scale_mode, int64_t n_blocks, int64_t blocks_per_tile, int q, int M,
+                           float clip, void* out_host, int out_dtype, void* codes_host);
 
 /*
  * E8-quantised gradient exchange, receive side.  The reference only plans this path
