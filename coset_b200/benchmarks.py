@@ -242,10 +242,14 @@ def bench_gradcomm():
     g = torch.Generator(device="cuda").manual_seed(1000 + rank)
     grad = torch.randn(n, device="cuda", generator=g) * 1e-3
     ex = E8GradientExchange(scale=500.0)
+    ex_peer = E8GradientExchange(scale=500.0, transport="peer")
     out = torch.empty_like(grad)
 
     def quantised():
         ex.all_reduce_mean(grad, out=out)
+
+    def quantised_peer():
+        ex_peer.all_reduce_mean(grad, out=out)
 
     ref = grad.clone()
 
@@ -256,7 +260,10 @@ def bench_gradcomm():
         ref.div_(world)
 
     res = {}
-    for name, fn in (("e8_exchange_ms", quantised), ("fp32_allreduce_ms", plain)):
+    cases = [("e8_exchange_ms", quantised), ("fp32_allreduce_ms", plain)]
+    if world > 1:
+        cases.insert(1, ("e8_exchange_peer_memory_ms", quantised_peer))
+    for name, fn in cases:
         for _ in range(3):
             fn()
         torch.cuda.synchronize()

@@ -19,16 +19,43 @@ namespace {
 
 constexpr int kThreads = 256;
 
-template <int DT>
+// Code streams of the ranks when they are NOT gathered into local memory first: one pointer per
+// rank into that rank's own buffer (peer memory, mapped into this process), read with plain loads
+// over NVLink.  first = the rank whose stream is read first (each rank starts at a different peer).
+constexpr int kMaxPeers = 16;
+struct PeerStreams {
+    const uint32_t* p[kMaxPeers];
+    int first;
+};
+
+template <int DT, bool PEERS>
 __global__ void __launch_bounds__(kThreads)
-k_decode_mean(const uint32_t* __restrict__ codes, int world, int64_t n, int64_t stride, float divisor,
+k_decode_mean(const uint32_t* __restrict__ codes, PeerStreams peers, int world, int64_t n, int64_t stride, float divisor,
               const uint2* __restrict__ table, void* __restrict__ out) {
     int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (b >= n) return;
     // 16-bit lanes: acc[0] = coordinates (0,2), acc[1] = (1,3), acc[2] = (4,6), acc[3] = (5,7)
     uint32_t acc[4] = {0u, 0u, 0u, 0u};
-    for (int r = 0; r < world; ++r) {
-        uint32_t code = __ldcs(codes + (int64_t)r * stride + b);
+    for (int r0 = 0; r0 < world; r0 += 4) {
+      uint32_t c4[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {  // up to four streams requested before the first table lookup
+        const int r = r0 + u;
+        c4[u] = 0u;
+        if (r < world) {
+            if (PEERS) {
+                int src = peers.first + r;
+                if (src >= world) src -= world;
+                c4[u] = __ldcs(peers.p[src] + b);
+            } else {
+                c4[u] = __ldcs(codes + (int64_t)r * stride + b);
+            }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (r0 + u >= world) break;
+        const uint32_t code = c4[u];
         uint2 t0 = __ldg(table + (code & 0xffffu));
         uint2 t1 = __ldg(table + (code >> 16));
         uint32_t lo = t0.x + 4u * t1.x, hi = t0.y + 4u * t1.y;  // biased bytes, each <= 90
@@ -36,6 +63,7 @@ k_decode_mean(const uint32_t* __restrict__ codes, int world, int64_t n, int64_t 
         acc[1] += (lo >> 8) & 0x00ff00ffu;
         acc[2] += hi & 0x00ff00ffu;
         acc[3] += (hi >> 8) & 0x00ff00ffu;
+      }
     }
     const int bias = 5 * e8::kTableBias * world;  // every rank contributes 7 + 4*7 to each lane
     int v[8];
@@ -68,9 +96,38 @@ extern "C" int coset_e8_decode_mean(const void* codes, int world, int64_t n_bloc
     if (!table) return COSET_E_STATE;
     float divisor = scale * (float)world;  // one float32 rounding, reproduced by the CPU recipe
     unsigned grid = (unsigned)((n_blocks + kThreads - 1) / kThreads);
+    PeerStreams none = {};
     if (out_dtype == COSET_DTYPE_F32)
-        k_decode_mean<0><<<grid, kThreads, 0, st>>>((const uint32_t*)codes, world, n_blocks, rank_stride_blocks, divisor, table, out);
+        k_decode_mean<0, false><<<grid, kThreads, 0, st>>>((const uint32_t*)codes, none, world, n_blocks, rank_stride_blocks, divisor, table, out);
     else
-        k_decode_mean<1><<<grid, kThreads, 0, st>>>((const uint32_t*)codes, world, n_blocks, rank_stride_blocks, divisor, table, out);
+        k_decode_mean<1, false><<<grid, kThreads, 0, st>>>((const uint32_t*)codes, none, world, n_blocks, rank_stride_blocks, divisor, table, out);
     return check_launch("e8_decode_mean");
+}
+
+extern "C" int coset_e8_decode_mean_peers(const void* const* rank_codes, int world, int rank, int64_t n_blocks, float scale,
+                                          void* out, int out_dtype, void* stream) {
+    if (world < 1 || world > kMaxPeers) return fail(COSET_E_BADARG, "world must be in 1..16 for the peer-memory form");
+    if (rank < 0 || rank >= world) return fail(COSET_E_BADARG, "rank outside the world");
+    if (n_blocks < 0) return fail(COSET_E_BADARG, "n_blocks is negative");
+    if (n_blocks == 0) return 0;
+    if (!rank_codes || !out) return fail(COSET_E_BADARG, "null pointer");
+    if (out_dtype != COSET_DTYPE_F32 && out_dtype != COSET_DTYPE_BF16) return fail(COSET_E_BADARG, "unknown out_dtype");
+    if (!aligned(out, 16)) return fail(COSET_E_ALIGN, "out must be 16-byte aligned");
+    if (!(scale == scale) || scale == 0.0f) return fail(COSET_E_BADARG, "scale must be a non-zero number");
+    PeerStreams peers = {};
+    for (int r = 0; r < world; ++r) {
+        if (!rank_codes[r] || !aligned(rank_codes[r], 4)) return fail(COSET_E_BADARG, "code stream %d is null or misaligned", r);
+        peers.p[r] = (const uint32_t*)rank_codes[r];
+    }
+    peers.first = rank;
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint2* table = residual_table_q4(st);
+    if (!table) return COSET_E_STATE;
+    float divisor = scale * (float)world;
+    unsigned grid = (unsigned)((n_blocks + kThreads - 1) / kThreads);
+    if (out_dtype == COSET_DTYPE_F32)
+        k_decode_mean<0, true><<<grid, kThreads, 0, st>>>(nullptr, peers, world, n_blocks, 0, divisor, table, out);
+    else
+        k_decode_mean<1, true><<<grid, kThreads, 0, st>>>(nullptr, peers, world, n_blocks, 0, divisor, table, out);
+    return check_launch("e8_decode_mean_peers");
 }

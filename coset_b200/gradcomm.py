@@ -8,10 +8,15 @@ prompts/design_instructions.md:104-110) but ships no code.  The exchange here is
     3. all-gather the packed codes (NCCL over NVLink; 1/8 of the float32 payload)
     4. one kernel decodes the W code streams and writes (sum_r x_hat_r) / (scale * W)
 
-Each rank only reads its own memory; the collective is a plain all_gather_into_tensor.  The
+With transport="nccl" (default) each rank only reads its own memory; the collective is a plain
+all_gather_into_tensor.  With transport="peer" steps 3 and 4 are ONE kernel: every rank encodes into a
+buffer in symmetric memory, a device-side barrier of torch's symmetric-memory handle orders "all
+encoded", and the decode kernel reads the W code streams straight from the peers' memory over NVLink
+(plain loads, no multicast) while it decodes -- no gathered copy is written or re-read.  The
 arithmetic is fixed (exact sum of reconstructions, one float32 division), so every rank obtains
-bit-identical averages and a CPU run of the same recipe reproduces them.
+bit-identical averages with either transport and a CPU run of the same recipe reproduces them.
 """
+import ctypes
 from typing import Optional
 
 import torch
@@ -49,12 +54,17 @@ class E8GradientExchange:
     keeps the two-level code away from overload.
     """
 
-    def __init__(self, group: Optional[dist.ProcessGroup] = None, scale: float = 500.0, codec=None):
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, scale: float = 500.0, codec=None,
+                 transport: str = "nccl"):
+        if transport not in ("nccl", "peer"):
+            raise ValueError("transport must be 'nccl' (all-gather, then decode) or 'peer' (decode from peer memory)")
         self.group = group
         self.scale = float(scale)
         self.codec = codec if codec is not None else CudaCodec()
+        self.transport = transport
         self._codes = None
         self._gathered = None
+        self._symm = None  # (n_blocks, buffer [2, n_blocks] int32, handle, parity)
 
     def _world(self):
         return dist.get_world_size(self.group) if dist.is_available() and dist.is_initialized() else 1
@@ -80,6 +90,13 @@ class E8GradientExchange:
         else:
             padded = flat.contiguous()
         world = self._world()
+        if self.transport == "peer" and world > 1:
+            res = self._all_reduce_mean_peer(padded, n_blocks, world)
+            res = res.view(-1)[:n_values]
+            if out is not None:
+                out.copy_(res)
+                return out
+            return res
         codes, gathered = self._buffers(n_blocks, world, flat.device)
         self.codec.encode(padded.view(n_blocks, 8), self.scale, codes)
         if world > 1:
@@ -93,6 +110,36 @@ class E8GradientExchange:
             out.copy_(res)
             return out
         return res
+
+
+def _peer_exchange(self, padded, n_blocks, world):
+    """Encode into this rank's half of a double-buffered symmetric allocation, barrier, decode from
+    every rank's buffer.  One barrier per call is enough: a rank overwrites half p only two calls
+    later, after the barrier of the call in between, which no rank passes before its own decode of
+    half p has been enqueued ahead of it on the same stream."""
+    import torch.distributed._symmetric_memory as symm
+    dev = padded.device
+    if self._symm is None or self._symm[0] != n_blocks:
+        buf = symm.empty(2, n_blocks, dtype=torch.int32, device=dev)
+        group = self.group if self.group is not None else dist.group.WORLD
+        hdl = symm.rendezvous(buf, group.group_name)
+        self._symm = [n_blocks, buf, hdl, 0]
+    _, buf, hdl, parity = self._symm
+    self._symm[3] = parity ^ 1
+    self.codec.encode(padded.view(n_blocks, 8), self.scale, buf[parity])
+    hdl.barrier(channel=parity)
+    res = torch.empty((n_blocks, 8), dtype=torch.float32, device=dev)
+    offset = parity * n_blocks * 4
+    ptrs = (ctypes.c_void_p * world)(*[int(p) + offset for p in hdl.buffer_ptrs])
+    with torch.cuda.device(dev):
+        rc = _lib.lib().coset_e8_decode_mean_peers(ctypes.cast(ptrs, ctypes.c_void_p), world, hdl.rank, n_blocks,
+                                                   float(self.scale), _lib.ptr(res), _lib.dtype_code(res, "out"),
+                                                   _lib.stream())
+    _lib.check(rc, "coset_e8_decode_mean_peers")
+    return res
+
+
+E8GradientExchange._all_reduce_mean_peer = _peer_exchange
 
 
 def e8_allreduce_hook(state: E8GradientExchange, bucket) -> torch.futures.Future[torch.Tensor]:

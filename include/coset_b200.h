@@ -168,6 +168,16 @@ int coset_e8_quantize_host(coset_host_ctx* ctx, const void* x_host, int x_dtype,
  */
 int coset_e8_decode_mean(const void* codes, int world, int64_t n_blocks, int64_t rank_stride_blocks,
                          float scale, void* out, int out_dtype, void* stream);
+/*
+ * The same receive side WITHOUT the all-gather: rank_codes[r] (host array of `world` device pointers)
+ * points at rank r's own code buffer, mapped into this process (peer / symmetric memory); the kernel
+ * reads the peers' streams with plain loads over NVLink while it decodes, starting at stream `rank`.
+ * The caller orders "every rank has finished encoding" before this call and "every rank has finished
+ * reading" before the buffers are overwritten (a device-side barrier of its communication library).
+ * world <= 16.  Same arithmetic, bit-identical result.
+ */
+int coset_e8_decode_mean_peers(const void* const* rank_codes, int world, int rank, int64_t n_blocks,
+                               float scale, void* out, int out_dtype, void* stream);
 
 /*
  * Code-domain ("vLUT") product for inference, small token counts:

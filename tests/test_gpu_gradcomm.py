@@ -138,3 +138,42 @@ def test_two_gpu_ddp_comm_hook(tmp_path):
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stderr[-2000:]
     assert "DDP_HOOK_OK" in res.stdout
+
+
+PEER_WORKER = r'''
+import os, sys
+import torch
+import torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from coset_b200.gradcomm import E8GradientExchange
+rank = int(os.environ["RANK"]); local = int(os.environ["LOCAL_RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(local)
+dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+via_nccl = E8GradientExchange(scale=500.0)
+via_peer = E8GradientExchange(scale=500.0, transport="peer")
+n_values = 8 * 50000 + 3
+for it in range(5):  # several calls in a row: both halves of the double buffer are reused
+    g = torch.Generator().manual_seed(1000 * it + rank)
+    grad = (torch.randn(n_values, generator=g) * 1e-3).cuda()
+    a = via_nccl.all_reduce_mean(grad)
+    b = via_peer.all_reduce_mean(grad)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b), f"transports differ at call {it}"
+dist.barrier()
+if rank == 0:
+    print("PEER_OK")
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_peer_memory_transport_equals_all_gather(tmp_path):
+    """The exchange that decodes straight from the peers' buffers returns the bits of the all-gather form."""
+    script = tmp_path / "peer_worker.py"
+    script.write_text(PEER_WORKER)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29623", str(script), ROOT]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert "PEER_OK" in res.stdout
