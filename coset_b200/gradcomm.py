@@ -64,7 +64,7 @@ class E8GradientExchange:
         self.transport = transport
         self._codes = None
         self._gathered = None
-        self._symm = None  # (n_blocks, buffer [2, n_blocks] int32, handle, parity)
+        self._symm = {}  # n_blocks -> [buffer [2, n_blocks] int32, handle, parity]; one entry per bucket size
 
     def _world(self):
         return dist.get_world_size(self.group) if dist.is_available() and dist.is_initialized() else 1
@@ -119,13 +119,14 @@ def _peer_exchange(self, padded, n_blocks, world):
     half p has been enqueued ahead of it on the same stream."""
     import torch.distributed._symmetric_memory as symm
     dev = padded.device
-    if self._symm is None or self._symm[0] != n_blocks:
+    if n_blocks not in self._symm:  # collective: every rank sees the same sequence of sizes
         buf = symm.empty(2, n_blocks, dtype=torch.int32, device=dev)
         group = self.group if self.group is not None else dist.group.WORLD
         hdl = symm.rendezvous(buf, group.group_name)
-        self._symm = [n_blocks, buf, hdl, 0]
-    _, buf, hdl, parity = self._symm
-    self._symm[3] = parity ^ 1
+        self._symm[n_blocks] = [buf, hdl, 0]
+    entry = self._symm[n_blocks]
+    buf, hdl, parity = entry
+    entry[2] = parity ^ 1
     self.codec.encode(padded.view(n_blocks, 8), self.scale, buf[parity])
     hdl.barrier(channel=parity)
     res = torch.empty((n_blocks, 8), dtype=torch.float32, device=dev)

@@ -152,9 +152,9 @@ dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 via_nccl = E8GradientExchange(scale=500.0)
 via_peer = E8GradientExchange(scale=500.0, transport="peer")
 n_values = 8 * 50000 + 3
-for it in range(5):  # several calls in a row: both halves of the double buffer are reused
+for it in range(6):  # several calls in a row: both halves of the double buffer are reused; two sizes alternate
     g = torch.Generator().manual_seed(1000 * it + rank)
-    grad = (torch.randn(n_values, generator=g) * 1e-3).cuda()
+    grad = (torch.randn(n_values if it % 2 == 0 else 8 * 777, generator=g) * 1e-3).cuda()
     a = via_nccl.all_reduce_mean(grad)
     b = via_peer.all_reduce_mean(grad)
     torch.cuda.synchronize()
