@@ -13,7 +13,9 @@ import warnings
 import numpy as np
 import torch
 
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
+ref_root = sys.argv[1]
 sys.path.insert(0, ref_root)
 sys.dont_write_bytecode = True
 warnings.filterwarnings("ignore")
