@@ -6,8 +6,7 @@
 // driver tests/legacy/test_one_sided_vlut_pytest.py:22-43); a table of 4^8 inner products per
 // 8 activations is 128 MB per token at K = 4096, so the GPU form keeps ONE table (the 65536
 // residuals r(b), 512 KB, L2/L1 resident), rebuilds the weight block in registers and multiplies:
-//     w = (r(b_0) + 4 r(b_1)) / beta        (same IEEE division as the training layer)
-//     y += <w, x_block>
+//     y += <r(b_0) + 4 r(b_1), x_block> / beta      (one scaling per block, after the inner product)
 // Small T ("GEMV" regime): memory-bound on the code stream, 4 B (+ scale) per 8 weights.
 // One warp owns one output row; lanes stride over the row's blocks (coalesced 128 B of codes per
 // step), keep TT token accumulators in registers and reduce with shuffles at the end.
@@ -55,23 +54,68 @@ k_vlut_gemv(const uint32_t* __restrict__ codes, const float* __restrict__ beta, 
 #pragma unroll
     for (int t = 0; t < TT; ++t) acc[t] = 0.0f;
     const int64_t row_base = (int64_t)row * kb;
-#pragma unroll 4
-    for (int blk = lane; blk < kb; blk += 32) {
-        uint32_t code = __ldcs(codes + row_base + blk);
-        float s = 1.0f;
-        if (MODE == COSET_SCALE_MUL_TILE) s = __ldg(beta + e8::tile_of(td, row_base + blk));
-        float v2[8], w[8];
-        e8::decode_q4m2_twice(code, table, v2);
-        e8::scale_twice<MODE == COSET_SCALE_MUL_TILE ? 2 : 0>(v2, s, w);
+    // Lanes stride over the row's blocks in groups of kGroup.  The codes (and scales) of the NEXT group are
+    // requested before the table entries of the current one, and all entries of a group before the
+    // first multiply, so a group costs one memory round trip (the longer of code fetch and gather)
+    // instead of one code fetch plus one gather per block.
+    constexpr int kGroup = 4;
+    uint32_t code_n[kGroup];
+    float s_n[kGroup];
+    auto fetch = [&](int blk0) {
 #pragma unroll
-        for (int t = 0; t < TT; ++t) {
-            if (t0 + t < T) {
-                float xv[8];
-                load_x8<XDT>(x, (int64_t)(t0 + t) * ldx + (int64_t)blk * 8, xv);
-                float a = acc[t];
+        for (int j = 0; j < kGroup; ++j) {
+            const int blk = blk0 + 32 * j;
+            code_n[j] = blk < kb ? __ldcs(codes + row_base + blk) : 0u;
+            s_n[j] = (MODE == COSET_SCALE_MUL_TILE && blk < kb) ? __ldg(beta + e8::tile_of(td, row_base + blk)) : 1.0f;
+        }
+    };
+    fetch(lane);
+    for (int blk0 = lane; blk0 < kb; blk0 += 32 * kGroup) {
+        uint32_t code_c[kGroup];
+        float s_c[kGroup];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) a = __fmaf_rn(w[i], xv[i], a);
-                acc[t] = a;
+        for (int j = 0; j < kGroup; ++j) { code_c[j] = code_n[j]; s_c[j] = s_n[j]; }
+        fetch(blk0 + 32 * kGroup);  // guarded per block: past the row's end it loads nothing
+        uint2 t_lo[kGroup], t_hi[kGroup];
+#pragma unroll
+        for (int j = 0; j < kGroup; ++j) {
+            t_lo[j] = __ldg(table + (code_c[j] & 0xffffu));
+            t_hi[j] = __ldg(table + (code_c[j] >> 16));
+        }
+#pragma unroll
+        for (int j = 0; j < kGroup; ++j) {
+            const int blk = blk0 + 32 * j;
+            if (blk < kb) {
+                // the block's inner product is formed on twice the (integer) reconstruction and scaled
+                // once by 0.5 / beta -- the look-up-table form of the product, 1 multiply per block and
+                // token instead of 8 exact divisions per block
+                float v2[8];
+                e8::twice_from_entries(t_lo[j], t_hi[j], v2);
+                const float half_inv = MODE == COSET_SCALE_MUL_TILE ? __fdividef(0.5f, s_c[j]) : 0.5f;
+                if (TT >= 4) {  // many tokens share the block: scale the 8 weights once instead
+                    float w[8];
+                    e8::scale_twice<MODE == COSET_SCALE_MUL_TILE ? 2 : 0>(v2, s_c[j], w);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v2[i] = w[i];
+                }
+#pragma unroll
+                for (int t = 0; t < TT; ++t) {
+                    if (t0 + t < T) {
+                        float xv[8];
+                        load_x8<XDT>(x, (int64_t)(t0 + t) * ldx + (int64_t)blk * 8, xv);
+                        if (TT >= 4) {
+                            float a = acc[t];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) a = __fmaf_rn(v2[i], xv[i], a);
+                            acc[t] = a;
+                        } else {
+                            float d = 0.0f;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) d = __fmaf_rn(v2[i], xv[i], d);
+                            acc[t] = __fmaf_rn(d, half_inv, acc[t]);
+                        }
+                    }
+                }
             }
         }
     }
