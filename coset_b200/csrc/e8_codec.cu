@@ -286,8 +286,7 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
     const int64_t stride = (int64_t)gridDim.x * kEncWarps * span;
     for (int64_t base = ((int64_t)blockIdx.x * kEncWarps + warp) * span; base < n; base += stride) {
         uint32_t code[kRowsPerIter];
-        int open_level[kRowsPerIter];  // 2 = finished, else the first level still open
-        bool need1[kRowsPerIter];
+        int open_level[kRowsPerIter];  // first level still open; 2 = finished, 3 = no block (past the end)
         float sc[kRowsPerIter];
         {
             // All rows are requested first; the level-0 path then runs row after row in straight-line
@@ -328,18 +327,21 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
                     if (!e8::level_fast_q4<false>(v[j], amax, code[j])) open_level[j] = 0;
                 }
                 // top level: origin unless max|x| > 1.96 or sum|x| > 7.96 (the level sees x / 4)
-                need1[j] = active && open_level[j] == 2 && !(amax <= 1.96f && s1 <= 7.96f);
+                if (open_level[j] == 2 && !(amax <= 1.96f && s1 <= 7.96f)) open_level[j] = 1;
+                if (!active) open_level[j] = 3;  // past the end: neither stored nor queued
             }
         }
+        bool any_open = false;
 #pragma unroll
         for (int j = 0; j < kRowsPerIter; ++j) {
-            const int64_t b = base + j * 32 + lane;
-            const bool active = b < n;
-            if (need1[j]) open_level[j] = 1;
-            if (active) {
-                if (open_level[j] == 2) {
-                    emit(b, code[j], sc[j]);
-                } else {
+            if (open_level[j] == 2) emit(base + j * 32 + lane, code[j], sc[j]);
+            any_open = any_open || open_level[j] < 2;
+        }
+        if (any_open) {  // rare: one branch per iteration keeps the queue code off the common path
+#pragma unroll
+            for (int j = 0; j < kRowsPerIter; ++j) {
+                if (open_level[j] < 2) {
+                    const int64_t b = base + j * 32 + lane;
                     const int pos = atomicAdd(&q_count[warp], 1);
                     q_meta[warp][0][pos] = (uint32_t)b;
                     q_meta[warp][1][pos] = (uint32_t)((uint64_t)b >> 32);
