@@ -288,6 +288,7 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
         uint32_t code[kRowsPerIter];
         int open_level[kRowsPerIter];  // first level still open; 2 = finished, 3 = no block (past the end)
         float sc[kRowsPerIter];
+        bool any_open = false;
         {
             // All rows are requested first; the level-0 path then runs row after row in straight-line
             // code, so the loads of the later rows and the FP32-heavy head of one row overlap the
@@ -329,13 +330,9 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
                 // top level: origin unless max|x| > 1.96 or sum|x| > 7.96 (the level sees x / 4)
                 if (open_level[j] == 2 && !(amax <= 1.96f && s1 <= 7.96f)) open_level[j] = 1;
                 if (!active) open_level[j] = 3;  // past the end: neither stored nor queued
+                if (open_level[j] == 2) emit(base + j * 32 + lane, code[j], sc[j]);
+                any_open = any_open || open_level[j] < 2;
             }
-        }
-        bool any_open = false;
-#pragma unroll
-        for (int j = 0; j < kRowsPerIter; ++j) {
-            if (open_level[j] == 2) emit(base + j * 32 + lane, code[j], sc[j]);
-            any_open = any_open || open_level[j] < 2;
         }
         if (any_open) {  // rare: one branch per iteration keeps the queue code off the common path
 #pragma unroll
