@@ -204,10 +204,14 @@ def bench_vlut_sharded():
     W = (torch.randn(n, n) * 0.02).cuda()
     beta = torch.full((n * n // 8,), 25.0, device="cuda")
     lin = ColumnParallelE8CodeLinear.from_weight(W, beta, 1, small_t_max=64)
+    lin_peer = ColumnParallelE8CodeLinear.from_weight(W, beta, 1, small_t_max=64, transport="peer")
     for T in (1, 16, 256, 4096):
         x = torch.randn(T, n, device="cuda").to(torch.bfloat16)
         res = {}
-        for name, fn in (("sharded_ms", lambda: lin(x)), ("local_product_ms", lambda: lin.local(x))):
+        cases = [("sharded_ms", lambda: lin(x)), ("local_product_ms", lambda: lin.local(x))]
+        if T <= 64:
+            cases.insert(1, ("sharded_peer_stores_ms", lambda: lin_peer(x)))
+        for name, fn in cases:
             for _ in range(5):
                 fn()
             torch.cuda.synchronize()

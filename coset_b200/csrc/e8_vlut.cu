@@ -41,11 +41,20 @@ __device__ __forceinline__ void load_x8<1>(const void* x, int64_t off, float (&v
     }
 }
 
+// Where a result row goes: one buffer, or (output-feature sharding over several GPUs) the same place
+// in the result buffer of every rank -- this rank's own and its peers' (peer memory, plain stores over
+// NVLink), which replaces the all-gather that would otherwise follow the product.
+constexpr int kMaxTargets = 16;
+struct Targets {
+    float* y[kMaxTargets];
+    int n;
+};
+
 template <int TT, int XDT, int MODE>
 __global__ void __launch_bounds__(kWarps * 32)
 k_vlut_gemv(const uint32_t* __restrict__ codes, const float* __restrict__ beta, e8::TileDiv td, int n_out, int kb,
             const void* __restrict__ x, int64_t ldx, int T, const float* __restrict__ bias,
-            const uint2* __restrict__ table, float* __restrict__ y, int64_t ldy) {
+            const uint2* __restrict__ table, Targets out, int64_t ldy) {
     int row = blockIdx.x * kWarps + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
     int t0 = blockIdx.y * TT;
@@ -124,13 +133,16 @@ k_vlut_gemv(const uint32_t* __restrict__ codes, const float* __restrict__ beta, 
         float a = acc[t];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-        if (lane == 0 && t0 + t < T) y[(int64_t)(t0 + t) * ldy + row] = a + (bias ? __ldg(bias + row) : 0.0f);
+        if (lane == 0 && t0 + t < T) {
+            const float r = a + (bias ? __ldg(bias + row) : 0.0f);
+            for (int k = 0; k < out.n; ++k) out.y[k][(int64_t)(t0 + t) * ldy + row] = r;
+        }
     }
 }
 
 template <int XDT, int MODE>
 void launch_gemv(int tt, dim3 grid, cudaStream_t st, const uint32_t* codes, const float* beta, e8::TileDiv td, int n_out,
-                 int kb, const void* x, int64_t ldx, int T, const float* bias, const uint2* table, float* y, int64_t ldy) {
+                 int kb, const void* x, int64_t ldx, int T, const float* bias, const uint2* table, const Targets& y, int64_t ldy) {
 #define GEMV_CASE(TT) k_vlut_gemv<TT, XDT, MODE><<<grid, kWarps * 32, 0, st>>>(codes, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy)
     switch (tt) {
         case 1: GEMV_CASE(1); break;
@@ -144,12 +156,11 @@ void launch_gemv(int tt, dim3 grid, cudaStream_t st, const uint32_t* codes, cons
 
 }  // namespace
 
-extern "C" int coset_e8_vlut_gemv(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
-                                  const void* x, int x_dtype, int64_t ldx, int T, const float* bias, float* y,
-                                  int64_t ldy, void* stream) {
+static int vlut_gemv_impl(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in, const void* x,
+                          int x_dtype, int64_t ldx, int T, const float* bias, const Targets& y, int64_t ldy, void* stream) {
     if (n_out < 0 || n_in < 0 || T < 0 || (n_in % 8) != 0) return fail(COSET_E_BADARG, "bad shape (n_in must be a multiple of 8)");
     if (n_out == 0 || T == 0) return 0;
-    if (!codes || !x || !y) return fail(COSET_E_BADARG, "null pointer");
+    if (!codes || !x) return fail(COSET_E_BADARG, "null pointer");
     if (x_dtype != COSET_DTYPE_F32 && x_dtype != COSET_DTYPE_BF16) return fail(COSET_E_BADARG, "unknown x_dtype");
     if (ldx < n_in || ldy < n_out) return fail(COSET_E_BADARG, "leading dimension too small");
     const int elem = x_dtype == COSET_DTYPE_F32 ? 4 : 2;
@@ -173,4 +184,27 @@ extern "C" int coset_e8_vlut_gemv(const void* codes, const float* beta, int64_t 
         else launch_gemv<1, 0>(tt, grid, st, c, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy);
     }
     return check_launch("e8_vlut_gemv");
+}
+
+extern "C" int coset_e8_vlut_gemv(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
+                                  const void* x, int x_dtype, int64_t ldx, int T, const float* bias, float* y,
+                                  int64_t ldy, void* stream) {
+    if (!y && n_out > 0 && T > 0) return fail(COSET_E_BADARG, "null pointer");
+    Targets t = {};
+    t.y[0] = y;
+    t.n = 1;
+    return vlut_gemv_impl(codes, beta, blocks_per_tile, n_out, n_in, x, x_dtype, ldx, T, bias, t, ldy, stream);
+}
+
+extern "C" int coset_e8_vlut_gemv_scatter(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
+                                          const void* x, int x_dtype, int64_t ldx, int T, const float* bias,
+                                          float* const* y_targets, int n_targets, int64_t ldy, void* stream) {
+    if (n_targets < 1 || n_targets > kMaxTargets || !y_targets) return fail(COSET_E_BADARG, "need 1..16 result buffers");
+    Targets t = {};
+    for (int k = 0; k < n_targets; ++k) {
+        if (!y_targets[k]) return fail(COSET_E_BADARG, "result buffer %d is null", k);
+        t.y[k] = y_targets[k];
+    }
+    t.n = n_targets;
+    return vlut_gemv_impl(codes, beta, blocks_per_tile, n_out, n_in, x, x_dtype, ldx, T, bias, t, ldy, stream);
 }

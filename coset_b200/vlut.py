@@ -164,11 +164,19 @@ class ColumnParallelE8CodeLinear(nn.Module):
     codes and scales of out_features / world rows, multiplies the (replicated) activations with
     them and the slices are exchanged with one all-gather of [T, out_features / world] floats.
 
-    The codes never cross the link; at T = 1 the all-gather is latency-bound."""
+    The codes never cross the link; at T = 1 the all-gather is latency-bound.
 
-    def __init__(self, local: E8CodeLinear, out_features: int, group=None):
+    transport="peer" (few tokens, T <= local.small_t_max): the product kernel writes every result row
+    straight into the result buffer of EVERY rank (symmetric memory, plain stores over NVLink), a
+    device-side barrier of the symmetric-memory handle follows, and no all-gather is issued."""
+
+    def __init__(self, local: E8CodeLinear, out_features: int, group=None, transport: str = "nccl"):
         super().__init__()
         import torch.distributed as dist
+        if transport not in ("nccl", "peer"):
+            raise ValueError("transport must be 'nccl' or 'peer'")
+        self.transport = transport
+        self._symm = {}  # T -> [buffer [2, T, out_features] float32, handle, parity]
         self.local = local
         self.group = group
         self.world = dist.get_world_size(group)
@@ -180,7 +188,8 @@ class ColumnParallelE8CodeLinear(nn.Module):
             raise ValueError(f"local shard has {local.out_features} rows, expected {hi - lo}")
 
     @classmethod
-    def from_weight(cls, weight: torch.Tensor, beta: torch.Tensor, blocks_per_tile: int, bias=None, group=None, **kw):
+    def from_weight(cls, weight: torch.Tensor, beta: torch.Tensor, blocks_per_tile: int, bias=None, group=None,
+                    transport: str = "nccl", **kw):
         """Quantise this rank's rows of a full [n_out, n_in] weight; beta holds the scales of the
         full weight (one per block for blocks_per_tile = 1, one per row for n_in / 8)."""
         import torch.distributed as dist
@@ -192,12 +201,45 @@ class ColumnParallelE8CodeLinear(nn.Module):
         b = beta.contiguous().view(-1)[lo * tiles_per_row:hi * tiles_per_row]
         local = E8CodeLinear.from_weight(weight[lo:hi].contiguous(), b, blocks_per_tile,
                                          bias[lo:hi] if bias is not None else None, **kw)
-        return cls(local, n_out, group)
+        return cls(local, n_out, group, transport)
+
+    def _forward_peer(self, x2: torch.Tensor) -> torch.Tensor:
+        import ctypes
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        T = x2.shape[0]
+        if T not in self._symm:  # collective: every rank sees the same sequence of token counts
+            buf = symm.empty(2, T, self.out_features, dtype=torch.float32, device=x2.device)
+            group = self.group if self.group is not None else dist.group.WORLD
+            self._symm[T] = [buf, symm.rendezvous(buf, group.group_name), 0]
+        entry = self._symm[T]
+        buf, hdl, parity = entry
+        entry[2] = parity ^ 1
+        lo, _ = out_feature_shard(self.out_features, self.world, self.rank)
+        offset = (parity * T * self.out_features + lo) * 4  # this rank's columns inside half `parity`
+        targets = (ctypes.c_void_p * self.world)(*[int(p) + offset for p in hdl.buffer_ptrs])
+        loc = self.local
+        x2 = x2.contiguous()
+        bias32 = loc.bias.to(torch.float32).contiguous() if loc.bias is not None else None
+        with torch.cuda.device(x2.device):
+            rc = _lib.lib().coset_e8_vlut_gemv_scatter(
+                _lib.ptr(loc.codes), _lib.ptr(loc.beta), loc.blocks_per_tile, loc.out_features, loc.in_features,
+                _lib.ptr(x2), _lib.dtype_code(x2, "x"), x2.stride(0), T, _lib.ptr(bias32) if bias32 is not None else None,
+                ctypes.cast(targets, ctypes.c_void_p), self.world, self.out_features, _lib.stream())
+        _lib.check(rc, "coset_e8_vlut_gemv_scatter")
+        hdl.barrier(channel=parity)  # all ranks have written their columns into this rank's buffer
+        # the half is written again two calls from now, after the barrier of the call in between
+        return buf[parity].clone()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
         lead = x.shape[:-1]
-        y_loc = self.local(x.reshape(-1, self.in_features)).contiguous()
+        x2 = x.reshape(-1, self.in_features)
+        if self.transport == "peer" and self.world > 1 and x2.shape[0] <= self.local.small_t_max:
+            y = self._forward_peer(x2)
+            y = y.to(x.dtype) if x.dtype != torch.float32 else y
+            return y.reshape(*lead, self.out_features)
+        y_loc = self.local(x2).contiguous()
         gathered = torch.empty(self.world * y_loc.numel(), dtype=y_loc.dtype, device=y_loc.device)
         dist.all_gather_into_tensor(gathered, y_loc.view(-1), group=self.group)
         return assemble_gathered(gathered.view(self.world, *y_loc.shape)).reshape(*lead, self.out_features)

@@ -193,6 +193,17 @@ int coset_e8_decode_mean_peers(const void* const* rank_codes, int world, int ran
 int coset_e8_vlut_gemv(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
                        const void* x, int x_dtype, int64_t ldx, int T, const float* bias, float* y,
                        int64_t ldy, void* stream);
+/*
+ * The same product with the result rows written into SEVERAL buffers at once: y_targets (host array of
+ * n_targets <= 16 device pointers) are the places of this rank's output-feature slice in the result
+ * buffer of every rank, its own and its peers' (peer / symmetric memory, plain stores over NVLink).
+ * With the weight sharded along the output features this replaces the all-gather after the product;
+ * the caller orders "all ranks have written" with a device-side barrier of its communication library.
+ */
+int coset_e8_vlut_gemv_scatter(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out,
+                               int n_in, const void* x, int x_dtype, int64_t ldx, int T,
+                               const float* bias, float* const* y_targets, int n_targets, int64_t ldy,
+                               void* stream);
 
 /*
  * Quantisation statistics of the q=4, M=2 codec over a tensor (one pass, deterministic):

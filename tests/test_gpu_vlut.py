@@ -114,9 +114,12 @@ for bpt, nbeta in ((1, n_out * n_in // 8), (n_in // 8, n_out)):
     bias = torch.randn(n_out).cuda()
     full = E8CodeLinear.from_weight(W, beta, bpt, bias)
     shard = ColumnParallelE8CodeLinear.from_weight(W, beta, bpt, bias)
+    peer = ColumnParallelE8CodeLinear.from_weight(W, beta, bpt, bias, transport="peer")
     for T in (1, 5, 200):
         x = torch.randn(T, n_in).cuda()
         assert torch.equal(shard(x), full(x)), (bpt, T)
+        for _ in range(3):  # several calls: both halves of the result buffer are reused
+            assert torch.equal(peer(x), full(x)), ("peer", bpt, T)
 torch.cuda.synchronize()
 if rank == 0:
     print("SHARD_OK")
