@@ -274,19 +274,29 @@ class HNLQLinearQAT(nn.Module):
             self.xmax_ema.mul_(m).add_((1 - m) * xmax)
 
     def _bounds(self):
-        """Adaptive (beta_min, beta_max) per tile (coset/core/layers.py:381-396)."""
-        qM = float(self.q ** self.M)
-        ginv = self._gamma_inv_host
-        beta_min = (self.Delta0 / qM) / (self.eta * ginv * self.sigma_ema)
-        beta_max_det = (self.Delta0 * (qM - 1)) / (2 * ginv * self.xmax_ema)
-        beta_max_prob = (self.Delta0 * (qM - 1)) / (2 * self.eta * ginv * self.sigma_ema)
-        beta_max = torch.minimum(beta_max_det, beta_max_prob)
-        beta_min = torch.minimum(beta_min, beta_max * 0.9)
-        return beta_min, beta_max
+        """Adaptive (beta_min, beta_max) per tile (coset/core/layers.py:381-396).
+
+        The bounds depend only on the two statistics buffers, which change once every 256 quantised
+        forwards, so they are kept until one of the buffers is written (in place or replaced) or a
+        hyper-parameter changes; the arithmetic and its order are the reference's."""
+        key = (self.sigma_ema._version, self.xmax_ema._version, self.sigma_ema.data_ptr(), self.xmax_ema.data_ptr(),
+               self.Delta0, self.eta, self.q, self.M)
+        if getattr(self, "_bounds_key", None) != key:
+            with torch.no_grad():
+                qM = float(self.q ** self.M)
+                ginv = self._gamma_inv_host
+                beta_min = (self.Delta0 / qM) / (self.eta * ginv * self.sigma_ema)
+                beta_max_det = (self.Delta0 * (qM - 1)) / (2 * ginv * self.xmax_ema)
+                beta_max_prob = (self.Delta0 * (qM - 1)) / (2 * self.eta * ginv * self.sigma_ema)
+                beta_max = torch.minimum(beta_max_det, beta_max_prob)
+                beta_min = torch.minimum(beta_min, beta_max * 0.9)
+                self._bounds_cache = (beta_min, beta_max, beta_max - beta_min)
+            self._bounds_key = key
+        return self._bounds_cache[0], self._bounds_cache[1]
 
     def _beta(self):
-        beta_min, beta_max = self._bounds()
-        return beta_min + torch.sigmoid(self.theta_beta) * (beta_max - beta_min)
+        beta_min, _ = self._bounds()
+        return beta_min + torch.sigmoid(self.theta_beta) * self._bounds_cache[2]
 
     # ------------------------------------------------------------------ quantised weights
     def _quantize_weights(self, out_dtype=torch.float32):
