@@ -92,3 +92,32 @@ def test_layer_bounds_and_state_on_cpu(golden_layer):
         layer(torch.zeros(2, 64))
     layer.disable_quantization()
     assert layer(torch.zeros(2, 64)).shape == (2, 48)
+
+
+def test_scale_bounds_cache_follows_the_statistics():
+    """The cached (beta_min, beta_max) are recomputed after any write to the statistics buffers and
+    after a hyper-parameter change, and equal the reference formula (coset/core/layers.py:381-396)."""
+    import torch
+    from coset_b200.core.e8 import create_e8_hnlq_linear
+    layer = create_e8_hnlq_linear(64, 8, device="cpu")
+
+    def formula():
+        qM = float(layer.q ** layer.M)
+        g = float(layer.gamma_inv)
+        bmin = (layer.Delta0 / qM) / (layer.eta * g * layer.sigma_ema)
+        bmax = torch.minimum((layer.Delta0 * (qM - 1)) / (2 * g * layer.xmax_ema),
+                             (layer.Delta0 * (qM - 1)) / (2 * layer.eta * g * layer.sigma_ema))
+        return torch.minimum(bmin, bmax * 0.9), bmax
+
+    for mutate in (lambda: None, lambda: layer.sigma_ema.mul_(3.0), lambda: layer.xmax_ema.add_(0.5),
+                   lambda: layer.sigma_ema.copy_(torch.rand(8) + 0.1), lambda: setattr(layer, "eta", 0.2)):
+        mutate()
+        got = layer._bounds()
+        again = layer._bounds()
+        assert got[0] is again[0]  # served from the cache while nothing changes
+        want = formula()
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+    beta = layer._beta()
+    assert torch.equal(beta, want[0] + torch.sigmoid(layer.theta_beta) * (want[1] - want[0]))
+    layer.load_state_dict({k: (v * 2 if k == "xmax_ema" else v) for k, v in layer.state_dict().items()})
+    assert torch.equal(layer._bounds()[1], formula()[1])
