@@ -320,6 +320,9 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
                 const float m1 = fmaxf(fmaxf(fabsf(v[j][3]), fabsf(v[j][4])), fabsf(v[j][5]));
                 const float amax = fmaxf(fmaxf(m0, m1), fmaxf(fabsf(v[j][6]), fabsf(v[j][7])));
                 const bool finite = (s1 - s1) == 0.0f;
+                // top level: origin unless max|x| > 1.96 or sum|x| > 7.96 (the level sees x / 4); decided
+                // here so that only one predicate, not amax and s1, lives across the level-0 path
+                const bool top_open = !(amax <= 1.96f && s1 <= 7.96f);
                 code[j] = 0;
                 open_level[j] = 2;
                 if (!finite) {
@@ -327,8 +330,7 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
                 } else if (!(amax <= 0.49f && s1 <= 1.99f)) {
                     if (!e8::level_fast_q4<false>(v[j], amax, code[j])) open_level[j] = 0;
                 }
-                // top level: origin unless max|x| > 1.96 or sum|x| > 7.96 (the level sees x / 4)
-                if (open_level[j] == 2 && !(amax <= 1.96f && s1 <= 7.96f)) open_level[j] = 1;
+                if (open_level[j] == 2 && top_open) open_level[j] = 1;
                 if (!active) open_level[j] = 3;  // past the end: neither stored nor queued
                 if (open_level[j] == 2) emit(base + j * 32 + lane, code[j], sc[j]);
                 any_open = any_open || open_level[j] < 2;
