@@ -43,7 +43,10 @@ struct CosetScan {
 };
 
 // Scan of one D8 coset: x is the (shifted) input, w = x + kMagic, d = x - rint(x).
-__device__ __forceinline__ void scan_coset(const float (&w)[8], const float (&d)[8], CosetScan& s) {
+// sA / sB: top bytes (sign bits) of d, coordinates (7..4) and (3..0).  GIVEN = false: gathered here and
+// returned; GIVEN = true: supplied by the caller.
+template <bool GIVEN>
+__device__ __forceinline__ void scan_coset(const float (&w)[8], const float (&d)[8], CosetScan& s, uint32_t& sA, uint32_t& sB) {
     uint32_t kb = max(umax3(__float_as_uint(d[0]) * 4u + 3u, __float_as_uint(d[1]) * 4u + 2u, __float_as_uint(d[2]) * 4u + 1u),
                       __float_as_uint(d[3]) * 4u);
     uint32_t ka = max(umax3(__float_as_uint(d[4]) * 4u + 3u, __float_as_uint(d[5]) * 4u + 2u, __float_as_uint(d[6]) * 4u + 1u),
@@ -53,8 +56,10 @@ __device__ __forceinline__ void scan_coset(const float (&w)[8], const float (&d)
     s.m = __uint_as_float(s.key >> 2);
     s.hA = gather_bytes<0x0040>(w[7], w[6], w[5], w[4]);
     s.hB = gather_bytes<0x0040>(w[3], w[2], w[1], w[0]);
-    uint32_t sA = gather_bytes<0x0073>(d[7], d[6], d[5], d[4]);
-    uint32_t sB = gather_bytes<0x0073>(d[3], d[2], d[1], d[0]);
+    if (!GIVEN) {
+        sA = gather_bytes<0x0073>(d[7], d[6], d[5], d[4]);
+        sB = gather_bytes<0x0073>(d[3], d[2], d[1], d[0]);
+    }
     uint32_t par = __float_as_uint(w[0]) ^ __float_as_uint(w[1]) ^ __float_as_uint(w[2]) ^ __float_as_uint(w[3]) ^
                    __float_as_uint(w[4]) ^ __float_as_uint(w[5]) ^ __float_as_uint(w[6]) ^ __float_as_uint(w[7]);
     s.odd = (par & 1u) != 0u;
@@ -99,8 +104,18 @@ __device__ __forceinline__ bool level_fast_q4(const float (&x)[8], float amax, u
         ds[i] = __fsub_rn(xs, __fsub_rn(ws[i], kMagic));
     }
     CosetScan s0, s1;
-    scan_coset(w, d, s0);
-    scan_coset(ws, ds, s1);
+    uint32_t sA, sB;
+    scan_coset<false>(w, d, s0, sA, sB);
+    if (EXACT_ROUND) {
+        scan_coset<false>(ws, ds, s1, sA, sB);
+    } else {
+        // Away from rounding ties (enforced below for this tier) x - 1/2 lies on the other side of its
+        // nearest integer than x does of its own: sign(ds_i) = !sign(d_i).  Blocks for which that
+        // fails have some |d_i| or |ds_i| at the tie threshold and are rejected by the guard.
+        sA = ~sA;
+        sB = ~sB;
+        scan_coset<true>(ws, ds, s1, sA, sB);
+    }
     if (!EXACT_ROUND && (!(s0.m < thr) || !(s1.m < thr))) return false;
     float delta = s1.sumsq - s0.sumsq;
     if (!(fabsf(delta) > 6.103515625e-05f)) return false;
