@@ -217,7 +217,7 @@ k_encode_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::T
 // the always-valid tiers.  This also serves an overloaded quantiser, where most blocks need the top
 // level: the queue then fills every iteration and is drained by full warps (running that level in
 // place for the lanes that need it was measured and is slower at every scale).
-constexpr int kRowsPerIter = 3;   // rows per lane and loop iteration (measured: 1 -> 0.464 ms, 2 -> 0.425, 3 -> 0.415, 4 -> 0.431)
+constexpr int kRowsPerIter = 3;   // rows per lane and loop iteration (measured on 2^25 blocks: 2 -> 0.395 ms, 3 -> 0.387, 4 -> 0.388)
 constexpr int kQueueSlots = 32 * (kRowsPerIter + 1);  // < 32 left after a drain + at most 32 per sub-step
 constexpr int kEncWarps = kThreads / 32;
 
