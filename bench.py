@@ -37,9 +37,18 @@ BYTES_PER_BLOCK_STEP = BYTES_PER_BLOCK_ENC + BYTES_PER_BLOCK_DEC
 BETA_HEADLINE = 25.0
 BETA_LITERAL = 0.021440971642732620
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one encode launch, from the ncu capture
-# summarised in profiles/, scaled to the full launch by the number of blocks.
-ENCODE_TRAFFIC_BYTES_PER_LAUNCH = 1.2723e9  # 8 x (151.12 + 7.92) MB: dram read + write of one ncu capture on 2^22 blocks, scaled to 2^25
+
+
+def encode_traffic_bytes(n_blocks):
+    """DRAM read + write bytes of one encode launch over n_blocks blocks: the counters of one profiler
+    capture of the same kernel on a smaller case (kept as data next to its summary), scaled by the
+    number of blocks.  None when no capture is on record."""
+    p = os.path.join(ROOT, "profiles", "codec_q4m2_bulk_fp32.json")
+    try:
+        d = json.load(open(p))
+        return (float(d["dram_bytes_read"]) + float(d["dram_bytes_write"])) * n_blocks / float(d["capture_blocks"])
+    except Exception:
+        return None
 
 
 def make_values(n_values, seed):
@@ -380,7 +389,7 @@ def main():
             "frac_of_hbm_peak": value / world / peak,
             "roofline": {"bound": "hbm", "kernel": "k_encode_q4m2_queued (dominant: %.0f%% of the step)" % (100 * per[0] / (per[0] + per[1])),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": ENCODE_TRAFFIC_BYTES_PER_LAUNCH * n / N_BLOCKS, "algorithmic_bytes_per_launch": n * BYTES_PER_BLOCK_ENC,
+                         "traffic": encode_traffic_bytes(n), "algorithmic_bytes_per_launch": n * BYTES_PER_BLOCK_ENC,
                          "peak_source": peak_src, "ms_per_launch": enc_ms,
                          "decode": {"achieved": n * BYTES_PER_BLOCK_DEC / (per[1] * 1e-3) / 1e9, "ms_per_launch": per[1]}},
             "clocks": clocks,

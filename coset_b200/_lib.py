@@ -87,6 +87,15 @@ def require_cuda(t, name):
     return t
 
 
+def require_float32(t, name):
+    """The weight-path kernels read their parameter as float32 rows; any other dtype would be
+    misread (and over-read), so it is refused before a launch."""
+    if t.dtype != torch.float32:
+        raise TypeError(f"{name} must be float32 (the fused weight kernels read float32 rows), got {t.dtype}; "
+                        "keep the layer's parameters in float32 and pass low-precision activations instead")
+    return t
+
+
 def dtype_code(t, name):
     if t.dtype == torch.float32:
         return DTYPE_F32

@@ -5,6 +5,8 @@ exist, pyproject.toml:67).  One JSON line per measurement:
     python -m coset_b200.benchmarks vlut       # code-domain matmul, W [4096, 4096], T in {1, 16, 256, 4096}
     python -m torch.distributed.run --nproc-per-node N -m coset_b200.benchmarks gradcomm
                                                # E8-quantised gradient exchange, BERT-base-shaped gradient
+    python -m coset_b200.benchmarks profile-gemv | profile-gemm
+                                               # small fixed cases of the two matmul kernels for a profiler capture
 
 Timing: CUDA events on the current stream, warm-up first, inputs resident on the device.
 Roofline denominators: MEASURED_PEAKS.json at the repository root when present, else the
@@ -297,9 +299,34 @@ def bench_gradcomm():
         dist.destroy_process_group()
 
 
+def profile_case(which):
+    """Small fixed cases for a profiler capture (W 4096 x 4096, per-block scales, bf16 tokens):
+    `profile-gemv` runs the few-token code-domain product five times at T = 1, `profile-gemm` the
+    fused tcgen05 dequant-GEMM three times at T = 2048 and checks its status word."""
+    from .vlut import E8CodeLinear, e8_dequant_gemm
+    torch.manual_seed(0)
+    n = 4096
+    W = (torch.randn(n, n) * 0.02).cuda()
+    beta = torch.full((n * n // 8,), 25.0, device="cuda")
+    lin = E8CodeLinear.from_weight(W, beta, 1)
+    if which == "profile-gemv":
+        x = torch.randn(1, n, device="cuda").to(torch.bfloat16)
+        for _ in range(5):
+            lin(x)
+    else:
+        x = torch.randn(2048, n, device="cuda").to(torch.bfloat16)
+        for _ in range(3):
+            e8_dequant_gemm(lin.codes, lin.beta, 1, x, None, check=True)
+    torch.cuda.synchronize()
+    print("ok")
+
+
 def main(argv=None):
     argv = sys.argv[1:] if argv is None else argv
     which = argv[0] if argv else "all"
+    if which in ("profile-gemv", "profile-gemm"):
+        profile_case(which)
+        return
     if which in ("qat", "all"):
         bench_qat()
     if which in ("vlut", "all"):

@@ -8,6 +8,7 @@ from .lattice import D4Lattice
 def d4_quantize(x: torch.Tensor, q=None) -> torch.Tensor:
     """The layer's quantize_fn for D4: the lattice projection (coset/core/d4/layers.py:44-46; q is
     accepted and unused, as in the reference).  x: [..., 4] float32 on a CUDA device."""
+    _lib.require_float32(x, "x")
     _lib.require_cuda(x, "x")
     if x.shape[-1] != 4:
         raise ValueError(f"Input dimension {tuple(x.shape)} doesn't match D4 dimension 4")
@@ -28,6 +29,7 @@ class _D4FakeQuant(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, weight, beta, blocks_per_tile, clip, out_dtype):
+        _lib.require_float32(weight, "weight")
         _lib.require_cuda(weight, "weight")
         w = weight.contiguous()
         b = beta.detach().to(torch.float32).contiguous().view(-1)

@@ -57,6 +57,7 @@ class _E8FakeQuant(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, weight, beta, blocks_per_tile, q, clip, out_dtype):
+        _lib.require_float32(weight, "weight")
         _lib.require_cuda(weight, "weight")
         w = weight.contiguous()
         b = beta.detach().to(torch.float32).contiguous().view(-1)

@@ -549,7 +549,7 @@ int coset_e8_encode(const void* x, int x_dtype, const float* scale, int scale_mo
     e8::TileDiv td = e8::make_tile_div(scale_mode == COSET_SCALE_MUL_TILE ? blocks_per_tile : 1, n_blocks);
     unsigned grid = grid_for(n_blocks);
     if (q == 4 && M == 2 && sem == COSET_SEM_CORE) {
-        // persistent warps: 16 CTAs per SM worth of grid (4 resident at a time) balances queue fill and tail
+        // persistent warps: at most kEncCtasPerSm CTAs per SM of grid (4 resident at a time)
         unsigned qgrid = encoder_grid(n_blocks);
         DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2_queued<DT, MODE, false, 0><<<qgrid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes, nullptr, nullptr, 0.0f))))
     } else if (q == 4 && M == 2) {

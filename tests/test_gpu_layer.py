@@ -60,31 +60,66 @@ def test_block_tiling_gradients(golden_layer, tag):
     assert np.abs(beta.grad.cpu().numpy() - want).max() <= 1e-5 * max(np.abs(want).max(), 1e-12) + 1e-12
 
 
+def expected_from_oracle(W, beta, theta, bmin, bmax, bias, x, t, blocks_per_tile, clip=2.0):
+    """Forward and backward of the reference graph clamp(ste(e8_quantize(W beta)) / beta) evaluated on
+    the CPU in float64 around the oracle's quantised weights (coset/core/layers.py:415-470, 472-484):
+    the straight-through estimator passes dWq where the clamp is inactive, dbeta collects
+    dWq * (W - Wq_unclipped) / beta per tile and dtheta = dbeta * sigmoid'(theta) * (bmax - bmin)."""
+    from oracle import oracle as O
+    o, i = W.shape
+    wq, un = O.fake_quant(W.reshape(-1, 8), beta.reshape(-1), blocks_per_tile, 4, clip)
+    wq64 = torch.from_numpy(wq.reshape(o, i).astype(np.float64)).requires_grad_(True)
+    x64 = torch.from_numpy(x.astype(np.float64)).requires_grad_(True)
+    b64 = torch.from_numpy(bias.astype(np.float64)).requires_grad_(True)
+    y = torch.nn.functional.linear(x64, wq64, b64)
+    ((y - torch.from_numpy(t.astype(np.float64))) ** 2).mean().backward()
+    g = wq64.grad.numpy().reshape(-1, 8)
+    inside = (np.abs(un.astype(np.float64)) <= clip)  # clamp passes the gradient on the closed interval
+    dW = (g * inside).reshape(o, i)
+    beta_blocks = np.repeat(beta.reshape(-1).astype(np.float64), blocks_per_tile)[:, None]
+    per_block = (g * inside * (W.reshape(-1, 8).astype(np.float64) - un.astype(np.float64)) / beta_blocks).sum(axis=1)
+    dbeta = per_block.reshape(-1, blocks_per_tile).sum(axis=1)
+    sg = 1.0 / (1.0 + np.exp(-theta.astype(np.float64)))
+    dtheta = dbeta * sg * (1.0 - sg) * (bmax.astype(np.float64) - bmin.astype(np.float64))
+    return {"Wq": wq.reshape(o, i), "y": y.detach().numpy(), "dW": dW, "dx": x64.grad.numpy(), "dbias": b64.grad.numpy(),
+            "dtheta": dtheta}
+
+
 @pytest.mark.parametrize("tag", ["small", "big", "mid"])
 def test_layer_forward_backward_row_tiling(golden_layer, tag):
+    """Every assertion always runs.  The layer's scale comes from the device sigmoid and may differ
+    from the fixture's CPU value in the last bit, so the expectation is (1) the oracle evaluated with
+    the layer's own scales, bit for bit for the weights and to 1e-5 for outputs and gradients, and
+    (2) the reference layer's fixture on every row whose scale and quantised weights are identical
+    to the fixture's, which must be nearly all rows."""
     g = golden_layer
     layer = make_layer(g, tag)
-    # beta is computed with device sigmoid; it may differ from the CPU value in the last bit
     beta = layer._beta().detach().cpu().numpy()
     assert rel(beta, g[f"{tag}_beta"]) < 1e-6
     x = dev(g[f"{tag}_x"]).requires_grad_(True)
     y = layer(x)
     ((y - dev(g[f"{tag}_t"])) ** 2).mean().backward()
     wq = layer._quantize_weights().detach().cpu().numpy()
-    # A row whose beta differs from the CPU value in the last bit rescales by that bit; a changed
-    # code would show as an O(1) jump, which must stay a rare boundary event.
-    want_wq = g[f"{tag}_Wq"]
-    jumps = (np.abs(wq - want_wq) > 1e-4 * np.maximum(np.abs(want_wq), 1e-3)).mean()
-    assert jumps < 2e-3, jumps
-    if jumps == 0:
-        assert rel(wq, want_wq) < 1e-6
-        assert rel(y.detach().cpu().numpy(), g[f"{tag}_y"]) < 1e-5
-        assert rel(layer.weight.grad.cpu().numpy(), g[f"{tag}_dW"]) < 1e-5
-        assert rel(x.grad.cpu().numpy(), g[f"{tag}_dx"]) < 1e-5
-        assert rel(layer.bias.grad.cpu().numpy(), g[f"{tag}_dbias"]) < 1e-5
-        want = g[f"{tag}_dtheta"]
-        got = layer.theta_beta.grad.cpu().numpy()
-        assert np.abs(got - want).max() <= 2e-4 * np.abs(want).max() + 1e-9
+    o, i = wq.shape
+    want = expected_from_oracle(g[f"{tag}_W"], beta, g[f"{tag}_theta"], g[f"{tag}_bmin"], g[f"{tag}_bmax"],
+                                g[f"{tag}_bias"], g[f"{tag}_x"], g[f"{tag}_t"], i // 8)
+    got = {"y": y.detach().cpu().numpy(), "dW": layer.weight.grad.cpu().numpy(), "dx": x.grad.cpu().numpy(),
+           "dbias": layer.bias.grad.cpu().numpy(), "dtheta": layer.theta_beta.grad.cpu().numpy()}
+    # (1) against the oracle with the layer's own scales
+    assert np.array_equal(bits(wq), bits(want["Wq"]))
+    for k in ("y", "dW", "dx", "dbias"):
+        assert rel(got[k], want[k]) < 1e-5, k
+    assert np.abs(got["dtheta"] - want["dtheta"]).max() <= 2e-4 * np.abs(want["dtheta"]).max() + 1e-9
+    # (2) against the reference layer's own outputs, row by row
+    same = (beta == g[f"{tag}_beta"]) & (bits(wq) == bits(g[f"{tag}_Wq"])).all(axis=1)
+    assert same.mean() >= 0.9, same.mean()
+    assert rel(got["y"][:, same], g[f"{tag}_y"][:, same]) < 1e-5
+    assert rel(got["dW"][same], g[f"{tag}_dW"][same]) < 1e-5
+    assert rel(got["dbias"][same], g[f"{tag}_dbias"][same]) < 1e-5
+    wt = g[f"{tag}_dtheta"]
+    assert np.abs(got["dtheta"][same] - wt[same]).max() <= 2e-4 * np.abs(wt).max() + 1e-9
+    if same.all():
+        assert rel(got["dx"], g[f"{tag}_dx"]) < 1e-5
 
 
 def test_state_dict_keys_and_warmup(golden_layer):

@@ -121,3 +121,19 @@ def test_scale_bounds_cache_follows_the_statistics():
     assert torch.equal(beta, want[0] + torch.sigmoid(layer.theta_beta) * (want[1] - want[0]))
     layer.load_state_dict({k: (v * 2 if k == "xmax_ema" else v) for k, v in layer.state_dict().items()})
     assert torch.equal(layer._bounds()[1], formula()[1])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float64])
+def test_low_precision_parameters_are_refused_before_any_launch(dtype):
+    """The fused weight kernels read float32 rows; a layer converted with .bfloat16() / .half() /
+    .double() must be refused on the host, not misread on the device."""
+    from coset_b200.core.layers import e8_fake_quantize
+    from coset_b200.core.d4.layers import d4_fake_quantize, d4_quantize
+    w8 = torch.zeros(4, 16, dtype=dtype)
+    beta = torch.ones(4)
+    with pytest.raises(TypeError, match="float32"):
+        e8_fake_quantize(w8, beta, 2)
+    with pytest.raises(TypeError, match="float32"):
+        d4_fake_quantize(w8, beta, 4)
+    with pytest.raises(TypeError, match="float32"):
+        d4_quantize(torch.zeros(4, 4, dtype=dtype))
