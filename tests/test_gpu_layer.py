@@ -90,8 +90,8 @@ def test_layer_forward_backward_row_tiling(golden_layer, tag):
     """Every assertion always runs.  The layer's scale comes from the device sigmoid and may differ
     from the fixture's CPU value in the last bit, so the expectation is (1) the oracle evaluated with
     the layer's own scales, bit for bit for the weights and to 1e-5 for outputs and gradients, and
-    (2) the reference layer's fixture on every row whose scale and quantised weights are identical
-    to the fixture's, which must be nearly all rows."""
+    (2) the reference layer's fixture on every row whose codes are the fixture's (a last-bit change of
+    the scale rescales a row by that bit; a changed code is an O(1) jump), which must be nearly all rows."""
     g = golden_layer
     layer = make_layer(g, tag)
     beta = layer._beta().detach().cpu().numpy()
@@ -111,8 +111,10 @@ def test_layer_forward_backward_row_tiling(golden_layer, tag):
         assert rel(got[k], want[k]) < 1e-5, k
     assert np.abs(got["dtheta"] - want["dtheta"]).max() <= 2e-4 * np.abs(want["dtheta"]).max() + 1e-9
     # (2) against the reference layer's own outputs, row by row
-    same = (beta == g[f"{tag}_beta"]) & (bits(wq) == bits(g[f"{tag}_Wq"])).all(axis=1)
-    assert same.mean() >= 0.9, same.mean()
+    want_wq = g[f"{tag}_Wq"]
+    same = (np.abs(wq - want_wq) <= 1e-6 * np.abs(want_wq)).all(axis=1)
+    assert same.mean() >= 0.95, same.mean()
+    assert (beta == g[f"{tag}_beta"]).mean() >= 0.5  # most scales are bit-identical to the CPU value
     assert rel(got["y"][:, same], g[f"{tag}_y"][:, same]) < 1e-5
     assert rel(got["dW"][same], g[f"{tag}_dW"][same]) < 1e-5
     assert rel(got["dbias"][same], g[f"{tag}_dbias"][same]) < 1e-5
