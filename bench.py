@@ -169,6 +169,153 @@ def cpu_port_throughput(x_cpu, beta_cpu, sample_blocks, threads, repeats=1):
     return sample_blocks * BYTES_PER_BLOCK_STEP / best / 1e9, best
 
 
+def parity_check(x_cpu, beta_cpu, codes, xhat, sample=1 << 16):
+    """The codes and reconstructions the timed kernels left in their output buffers, compared bit for
+    bit with the CPU oracle on the first `sample` blocks (outside the timed region)."""
+    import numpy as np
+    from oracle import oracle as O
+    k = min(sample, x_cpu.shape[0])
+    digits = O.encode(x_cpu[:k].numpy(), beta=beta_cpu[:k].numpy(), scale_mode=2, blocks_per_tile=1, threads=os.cpu_count() or 1)
+    want_x = O.decode(digits, beta=beta_cpu[:k].numpy(), scale_mode=2, blocks_per_tile=1, threads=os.cpu_count() or 1)
+    got_c = codes[:k].view(torch.int32).view(-1).cpu().numpy().view(np.uint32)
+    got_x = xhat[:k].cpu().numpy()
+    return {"sample_blocks": k, "codes_bit_exact": bool(np.array_equal(got_c, O.pack_q4(digits))),
+            "reconstruction_bit_exact": bool(np.array_equal(got_x.view(np.uint32), (want_x + np.float32(0)).view(np.uint32))),
+            "against": "CPU oracle (C restatement of coset.core.e8)"}
+
+
+def gradient_exchange_detail(rank, world, iters=10):
+    """E8-quantised gradient exchange on the BERT-base-shaped gradient (109 482 240 values, N(0, 1e-3),
+    seed 1000 + rank, scale 500), per transport: time (CUDA events, max over ranks), the phases of the
+    all-gather form, the plain float32 all-reduce beside it, and a bit-for-bit check of rank 0's result
+    against the CPU recipe on every 64th block."""
+    import numpy as np
+    import torch.distributed as dist
+    from coset_b200.gradcomm import E8GradientExchange, bert_base_gradient_numel
+    n_values = bert_base_gradient_numel()
+    n_blocks = n_values // 8
+    scale = 500.0
+    g = torch.Generator().manual_seed(1000 + rank)
+    grad = (torch.randn(n_values, generator=g) * 1e-3).cuda()
+    out = torch.empty_like(grad)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # the CPU recipe on every 64th block needs every rank's sample of the input
+    sample = grad.view(n_blocks, 8)[::64].contiguous()
+    samples = torch.empty((world,) + tuple(sample.shape), dtype=torch.float32, device="cuda")
+    dist.all_gather_into_tensor(samples.view(-1), sample.view(-1))
+    want = None
+    if rank == 0:
+        from oracle import oracle as O
+        total = None
+        for r in range(world):
+            # the exchange's encode: x * scale in float32, clamped to +-3.9 (saturating encode), then the codec
+            xs = (samples[r].cpu().numpy() * np.float32(scale)).astype(np.float32)
+            d = O.encode(np.clip(xs, np.float32(-3.9), np.float32(3.9)), threads=os.cpu_count() or 1)
+            xh = O.decode(d)
+            total = xh if total is None else (total + xh).astype(np.float32)
+        want = (total / np.float32(np.float32(scale) * np.float32(world))).astype(np.float32)
+
+    res = {"values": n_values, "scale": scale, "wire_bytes_sent_per_rank": n_blocks * 4,
+           "wire_bytes_received_per_rank": (world - 1) * n_blocks * 4}
+    ref = grad.clone()
+
+    def plain():
+        ref.copy_(grad)
+        dist.all_reduce(ref)
+        ref.div_(world)
+    res["fp32_allreduce_ms"] = timed(plain)
+    for transport in ("nccl", "peer"):
+        ex = E8GradientExchange(scale=scale, transport=transport)
+        ms = timed(lambda: ex.all_reduce_mean(grad, out=out))
+        rec = {"ms": ms, "gradient_GBps_per_gpu": n_values * 4 / (ms * 1e-3) / 1e9,
+               "nvlink_rx_GBps": (world - 1) * n_blocks * 4 / (ms * 1e-3) / 1e9,
+               "frac_of_900GBps": (world - 1) * n_blocks * 4 / (ms * 1e-3) / 1e9 / 900.0,
+               "speedup_vs_fp32_allreduce": res["fp32_allreduce_ms"] / ms}
+        if transport == "nccl":  # phases: encode | all-gather | decode-and-average (events on this rank)
+            ex.phase_events = []
+            for _ in range(5):
+                ex.all_reduce_mean(grad, out=out)
+            torch.cuda.synchronize()
+            ev, ph = ex.phase_events, [0.0, 0.0, 0.0]
+            for i in range(0, len(ev), 4):
+                for j in range(3):
+                    ph[j] += ev[i + j].elapsed_time(ev[i + j + 1]) / (len(ev) // 4)
+            ex.phase_events = None
+            t = torch.tensor(ph, dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            rec["phases_ms"] = dict(zip(("encode", "all_gather", "decode_mean"), [float(v) for v in t]))
+            rec["bound_by"] = max(rec["phases_ms"], key=rec["phases_ms"].get)
+        ex.all_reduce_mean(grad, out=out)
+        torch.cuda.synchronize()
+        if rank == 0:
+            got = out.view(n_blocks, 8)[::64].cpu().numpy()
+            rec["matches_cpu_recipe"] = bool(np.array_equal((got + np.float32(0)).view(np.uint32), (want + np.float32(0)).view(np.uint32)))
+        res[transport] = rec
+        del ex
+    return res
+
+
+def column_parallel_detail(rank, world, iters=20):
+    """Code-domain product [4096, 4096] sharded along the output features over the ranks: per token
+    count the time of the sharded layer (all-gather of the outputs, or peer stores for few tokens), the
+    local product alone, and a bit-for-bit comparison with the unsharded layer on the same device."""
+    import torch.distributed as dist
+    from coset_b200.vlut import ColumnParallelE8CodeLinear, E8CodeLinear
+    torch.manual_seed(0)
+    n = 4096
+    W = (torch.randn(n, n) * 0.02).cuda()
+    beta = torch.full((n * n // 8,), 25.0, device="cuda")
+    full = E8CodeLinear.from_weight(W, beta, 1)
+    lin = ColumnParallelE8CodeLinear.from_weight(W, beta, 1)
+    lin_peer = ColumnParallelE8CodeLinear.from_weight(W, beta, 1, transport="peer")
+    out = {}
+    for T in (1, 16, 256, 4096):
+        x = torch.randn(T, n, device="cuda").to(torch.bfloat16)
+        cases = [("all_gather_ms", lambda: lin(x)), ("local_product_ms", lambda: lin.local(x))]
+        if T <= lin.local.small_t_max:
+            cases.append(("peer_stores_ms", lambda: lin_peer(x)))
+        rec = {}
+        for name, fn in cases:
+            for _ in range(5):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b) / iters], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            rec[name] = float(t.item())
+        same = torch.equal(lin(x), full(x))
+        if T <= lin.local.small_t_max:
+            same = same and torch.equal(lin_peer(x), full(x))
+        flag = torch.tensor([1 if same else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        rec["matches_unsharded"] = bool(int(flag.item()))
+        rec["tokens_per_s"] = T / (min(v for k, v in rec.items() if k in ("all_gather_ms", "peer_stores_ms")) * 1e-3)
+        rec["gathered_bytes_per_rank"] = T * n // world * 4
+        out[f"T={T}"] = rec
+    return out
+
+
 def base_line(args, world):
     return {
         "metric": "E8 HNLQ encode+decode GB/s (% HBM peak)",
@@ -226,6 +373,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-detail", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-comm", action="store_true", help="skip the gradient-exchange / column-parallel section of a multi-GPU run")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -366,6 +514,27 @@ def main():
         detail["literal_beta_theta0"] = {"beta": BETA_LITERAL, "encode_GBps": gbs(p[0], 40), "decode_GBps": gbs(p[1], 40),
                                          "encode+decode_GBps": gbs(p[0] + p[1], 80), "note": "all codes are zero at this scale"}
         enc(); dec()  # restore headline buffers
+        if world == 1:
+            # the other two workloads of the metric (quantized-linear tokens/s), one GPU
+            from coset_b200 import benchmarks as B
+            keep = ("tiling", "ms_per_step", "tokens_per_s", "graph_ms_per_step", "graph_tokens_per_s", "fake_quant_fwd_ms",
+                    "fake_quant_frac_of_hbm")
+            detail["qat"] = {("literal_std0.02" if r["weights"].startswith("literal") else "std20"): {k: r[k] for k in keep}
+                             for r in B.iter_qat(cases=((0.02, "row"), (20.0, "row")))}
+            detail["qat"]["workload"] = "E8HNLQLinear QAT step: W [3072, 768], 4096 bf16 tokens, forward + backward"
+            detail["vlut"] = [{k: r[k] for k in ("T", "ms", "tokens_per_s", "path", "timing", "bound", "frac") if k in r} |
+                              ({"TFLOPs": r["TFLOPs"]} if "TFLOPs" in r else {"GBps": r["GBps"]})
+                              for r in B.iter_vlut(tilings=("block",))]
+
+    # ---- parity of what the timed kernels produced (rank 0, sample vs the CPU oracle)
+    parity = parity_check(x_cpu, beta_cpu, codes, xhat) if rank == 0 and not args.no_cpu else None
+
+    # ---- the paths that communicate (multi-GPU runs only; every rank takes part)
+    comm = None
+    if world > 1 and not args.no_comm:
+        del x, xhat, codes
+        torch.cuda.empty_cache()
+        comm = {"gradcomm": gradient_exchange_detail(rank, world), "vlut_column_parallel": column_parallel_detail(rank, world)}
 
     # ---- CPU baseline (rank 0, single-GPU run only)
     cpu = None
@@ -387,7 +556,7 @@ def main():
             "ms_per_step": total_ms / args.steps,
             "gpu_launches": 2 * args.steps,
             "frac_of_hbm_peak": value / world / peak,
-            "roofline": {"bound": "hbm", "kernel": "k_encode_q4m2_queued (dominant: %.0f%% of the step)" % (100 * per[0] / (per[0] + per[1])),
+            "roofline": {"bound": "hbm", "kernel": "encode pass = k_encode_q4m2_main + its fix-up launch k_encode_q4m2_fix (dominant: %.0f%% of the step)" % (100 * per[0] / (per[0] + per[1])),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": encode_traffic_bytes(n), "algorithmic_bytes_per_launch": n * BYTES_PER_BLOCK_ENC,
                          "peak_source": peak_src, "ms_per_launch": enc_ms,
@@ -395,8 +564,11 @@ def main():
             "clocks": clocks,
             "e2e": e2e,
             "cpu_baseline": cpu,
+            "parity": parity,
             "detail": detail,
         })
+        if comm is not None:
+            line["detail"].update(comm)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libcoset_b200.so")
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
 SCALE_NONE, SCALE_DIV_SCALAR, SCALE_MUL_TILE = 0, 1, 2
-SEM_CORE, SEM_REF, SEM_CORE_LITERAL = 0, 1, 2
+SEM_CORE, SEM_REF, SEM_CORE_LITERAL, SEM_CORE_SATURATE = 0, 1, 2, 3
 
 _lib = None
 
@@ -36,7 +36,8 @@ SIGNATURES = {
     "coset_e8_decode_host": [_vp, _vp, _vp, _i32, _i64, _i64, _i32, _i32, _vp, _i32],
     "coset_e8_quantize_host": [_vp, _vp, _i32, _vp, _i32, _i64, _i64, _i32, _i32, _f32, _vp, _i32, _vp],
     "coset_e8_decode_mean": [_vp, _i32, _i64, _i64, _f32, _vp, _i32, _vp],
-    "coset_e8_decode_mean_peers": [_vp, _i32, _i32, _i64, _f32, _vp, _i32, _vp],
+    "coset_e8_decode_mean_peers": [_vp, _i32, _i32, _i64, _f32, _vp, _i32, _vp, _vp],
+    "coset_peer_signal_wait": [_vp, _i32, _i32, ctypes.c_uint32, _i32, _vp, _vp],
     "coset_e8_vlut_gemv": [_vp, _vp, _i64, _i32, _i32, _vp, _i32, _i64, _i32, _vp, _vp, _i64, _vp],
     "coset_e8_vlut_gemv_scatter": [_vp, _vp, _i64, _i32, _i32, _vp, _i32, _i64, _i32, _vp, _vp, _i32, _i64, _vp],
     "coset_e8_quant_stats_scratch_bytes": [_i64],

@@ -90,7 +90,8 @@ def graph_step_time(layer, x, t):
     return cuda_time(lambda: g.replay())
 
 
-def bench_qat():
+def iter_qat(cases=None):
+    """Yields one record per (weights, tiling) case of the QAT step benchmark."""
     from .core.e8 import create_e8_hnlq_linear
     from .core.layers import e8_fake_quantize
     hbm, tf, src = peaks()
@@ -98,40 +99,52 @@ def bench_qat():
     tokens, d_in, d_out = 4096, 768, 3072
     x = torch.randn(tokens, d_in, device="cuda").to(torch.bfloat16)
     t = torch.randn(tokens, d_out, device="cuda").to(torch.bfloat16)
-    for tag, std in (("literal std=0.02 (all weights quantise to 0)", 0.02), ("std=20 (55% non-zero weights)", 20.0)):
-        for tiling in ("row", "block"):
-            layer = create_e8_hnlq_linear(d_in, d_out, q=4, M=2, tiling=tiling, init_kwargs={"std": std}, device="cuda")
+    all_cases = [(tag, std, tiling)
+                 for tag, std in (("literal std=0.02 (all weights quantise to 0)", 0.02), ("std=20 (55% non-zero weights)", 20.0))
+                 for tiling in ("row", "block")]
+    for tag, std, tiling in all_cases:
+        if cases is not None and (std, tiling) not in cases:
+            continue
+        layer = create_e8_hnlq_linear(d_in, d_out, q=4, M=2, tiling=tiling, init_kwargs={"std": std}, device="cuda")
 
-            def step():
-                layer.zero_grad(set_to_none=True)
-                y = layer(x)
-                ((y - t).float() ** 2).mean().backward()
+        def step():
+            layer.zero_grad(set_to_none=True)
+            y = layer(x)
+            ((y - t).float() ** 2).mean().backward()
 
-            ms = cuda_time(step)
-            ms_graph = graph_step_time(layer, x, t)
-            beta = layer._beta().detach()
-            bpt = layer.blocks_per_row if tiling == "row" else 1
-            w = layer.weight.detach()
-            fq = cuda_time(lambda: e8_fake_quantize(w, beta, bpt, 4, 2.0, torch.bfloat16))
-            n_blocks = w.numel() // 8
-            fq_bytes = n_blocks * (32 + 16 + 4) + beta.numel() * 4  # fp32 in, bf16 out, codes out, scales
-            print(json.dumps({
-                "bench": "qat_step", "weights": tag, "tiling": tiling, "tokens": tokens, "shape": [d_out, d_in],
-                "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3),
-                "graph_ms_per_step": ms_graph, "graph_tokens_per_s": tokens / (ms_graph * 1e-3),
-                "note": "eager steps are bound by the Python / launch path; the graph replays the same forward + backward",
-                "gemm_tflops_equiv": 3 * 2 * tokens * d_in * d_out / (ms * 1e-3) / 1e12,
-                "fake_quant_fwd_ms": fq, "fake_quant_fwd_GBps": fq_bytes / (fq * 1e-3) / 1e9,
-                "fake_quant_frac_of_hbm": fq_bytes / (fq * 1e-3) / 1e9 / hbm, "peaks": src}), flush=True)
+        ms = cuda_time(step)
+        ms_graph = graph_step_time(layer, x, t)
+        beta = layer._beta().detach()
+        bpt = layer.blocks_per_row if tiling == "row" else 1
+        w = layer.weight.detach()
+        fq = cuda_time(lambda: e8_fake_quantize(w, beta, bpt, 4, 2.0, torch.bfloat16))
+        n_blocks = w.numel() // 8
+        fq_bytes = n_blocks * (32 + 16 + 4) + beta.numel() * 4  # fp32 in, bf16 out, codes out, scales
+        yield ({
+            "bench": "qat_step", "weights": tag, "tiling": tiling, "tokens": tokens, "shape": [d_out, d_in],
+            "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3),
+            "graph_ms_per_step": ms_graph, "graph_tokens_per_s": tokens / (ms_graph * 1e-3),
+            "note": "eager steps are bound by the Python / launch path; the graph replays the same forward + backward",
+            "gemm_tflops_equiv": 3 * 2 * tokens * d_in * d_out / (ms * 1e-3) / 1e12,
+            "fake_quant_fwd_ms": fq, "fake_quant_fwd_GBps": fq_bytes / (fq * 1e-3) / 1e9,
+            "fake_quant_frac_of_hbm": fq_bytes / (fq * 1e-3) / 1e9 / hbm, "peaks": src})
 
 
-def bench_vlut():
+def bench_qat():
+    for rec in iter_qat():
+        print(json.dumps(rec), flush=True)
+
+
+def iter_vlut(tilings=("block", "row")):
+    """Yields one record per (tiling, T, path) of the code-domain product benchmark."""
     from .vlut import E8CodeLinear
     hbm, tf, src = peaks()
     torch.manual_seed(0)
     n = 4096
     W = (torch.randn(n, n) * 0.02).cuda()
     for tiling, bpt, nbeta in (("block", 1, n * n // 8), ("row", n // 8, n)):
+        if tiling not in tilings:
+            continue
         beta = torch.full((nbeta,), 25.0, device="cuda")
         lin = E8CodeLinear.from_weight(W, beta, bpt, small_t_max=64)
         wbytes = n * n // 8 * 4 + nbeta * 4
@@ -149,15 +162,20 @@ def bench_vlut():
                 rec.update({"bound": "hbm", "GBps": by / (ms * 1e-3) / 1e9, "frac": by / (ms * 1e-3) / 1e9 / hbm})
             else:
                 rec.update({"bound": "tensor", "TFLOPs": flops / (ms * 1e-3) / 1e12, "frac": flops / (ms * 1e-3) / 1e12 / tf})
-            print(json.dumps(rec), flush=True)
+            yield rec
             if T > 64:
                 from .vlut import e8_dequant_gemm
                 e8_dequant_gemm(lin.codes, lin.beta, bpt, x, None, check=True)
                 ms2 = graph_time(lambda: e8_dequant_gemm(lin.codes, lin.beta, bpt, x, None), calls=10, replays=5)
-                print(json.dumps({"bench": "vlut_matmul", "tiling": tiling, "T": T, "shape": [n, n], "ms": ms2,
-                                  "tokens_per_s": T / (ms2 * 1e-3), "path": "fused tcgen05 dequant-GEMM (no dense weight in HBM)",
-                                  "timing": "CUDA graph replay", "bound": "tensor", "TFLOPs": flops / (ms2 * 1e-3) / 1e12,
-                                  "frac": flops / (ms2 * 1e-3) / 1e12 / tf, "peaks": src}), flush=True)
+                yield {"bench": "vlut_matmul", "tiling": tiling, "T": T, "shape": [n, n], "ms": ms2,
+                       "tokens_per_s": T / (ms2 * 1e-3), "path": "fused tcgen05 dequant-GEMM (no dense weight in HBM)",
+                       "timing": "CUDA graph replay", "bound": "tensor", "TFLOPs": flops / (ms2 * 1e-3) / 1e12,
+                       "frac": flops / (ms2 * 1e-3) / 1e12 / tf, "peaks": src}
+
+
+def bench_vlut():
+    for rec in iter_vlut():
+        print(json.dumps(rec), flush=True)
 
 
 def bench_d4():

@@ -8,9 +8,11 @@
 #include <stdarg.h>
 
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "e8_fast.cuh"
+#include "e8_fast2.cuh"
 #include "e8_io.cuh"
 #include "e8_literal.cuh"
 
@@ -206,20 +208,25 @@ k_encode_q4m2(const void* __restrict__ x, const float* __restrict__ scale, e8::T
 // Queued encoder (the production path for q=4, M=2).
 //
 // Warps are persistent; one loop iteration of a warp covers kRowsPerIter * 32 consecutive blocks,
-// one row per lane and sub-step.  Every lane runs the cheap rint-based level-0 path; whatever that
-// path cannot finish -- a block on a rounding tie, a block whose top level is not the origin, a
-// non-finite block -- is NOT handled in place (that would idle the other 31 lanes for hundreds of
-// instructions): the lane appends the block's index, its code so far and its first open level to
-// a per-warp queue in shared memory (a shared-memory atomic hands out the slot, so no warp-wide
-// vote sits on the common path).  Once per iteration the warp looks at the queue length; with 32
-// or more entries (and at the end) it drains 32 of them with all lanes busy: every lane reads the
-// row of its entry again -- one memory round trip per 32 deferred blocks -- and completes it with
-// the always-valid tiers.  This also serves an overloaded quantiser, where most blocks need the top
-// level: the queue then fills every iteration and is drained by full warps (running that level in
-// place for the lanes that need it was measured and is slower at every scale).
-constexpr int kRowsPerIter = 3;   // rows per lane and loop iteration (measured on 2^25 blocks: 2 -> 0.395 ms, 3 -> 0.387, 4 -> 0.388)
+// one row per lane and sub-step.  Every lane runs the cheapest tier (level_fast2_q4: one rounding
+// pass, both cosets from it, digits on the FP32 pipe) behind one pre-test, max|x| <= 1.96 and
+// sum|x| <= 7.96, which makes the top level the origin and bounds every quantity of that tier.
+// Whatever the tier cannot prove -- a block near a rounding tie, a block whose top level is not the
+// origin, a non-finite block -- is NOT handled in place (that would idle the other 31 lanes for
+// hundreds of instructions): the lane appends the block's index to a per-warp queue in shared memory
+// (a shared-memory atomic hands out the slot, so no warp-wide vote sits on the common path).  Once
+// per iteration the warp looks at the queue length; with 32 or more entries (and at the end) it
+// drains 32 of them with all lanes busy: every lane reads the row of its entry again -- one memory
+// round trip per 32 deferred blocks -- and encodes it from scratch with the always-valid tiers.
+// This also serves an overloaded quantiser, where most blocks need the top level: the queue then
+// fills every iteration and is drained by full warps.
+// SAT: every scaled coordinate is first clamped to +-kSaturate, which keeps the two-level code from
+// wrapping around (the top level stays the origin); only deferred blocks can exceed the bound, so the
+// clamp costs nothing on the common path.
+constexpr int kRowsPerIter = 3;   // rows per lane and loop iteration
 constexpr int kQueueSlots = 32 * (kRowsPerIter + 1);  // < 32 left after a drain + at most 32 per sub-step
 constexpr int kEncWarps = kThreads / 32;
+constexpr float kSaturate = 3.9f;  // 8 * 3.9 / 4 < 7.96 and 3.9 / 4 < 1.96: level 1 of a clamped block is the origin
 
 // CTAs of the queued encoder: enough for every warp to get one iteration, at most kEncCtasPerSm per SM.
 constexpr int kEncCtasPerSm = 12;
@@ -233,11 +240,11 @@ inline unsigned encoder_grid(int64_t n_blocks) {
 // RECON = false: codes only (e8_encode).  RECON = true: the fused round trip -- every finished code is
 // decoded through the residual table, unscaled, clamped and written as [n, 8] of type DTO; the
 // packed code is stored only if `codes` is not null (e8_quantize / the layer's weight path).
-template <int DT, int MODE, bool RECON, int DTO>
+template <int DT, int MODE, bool RECON, int DTO, bool SAT>
 __global__ void __launch_bounds__(kThreads, 4)
 k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
                      uint32_t* __restrict__ codes, const uint2* __restrict__ table, void* __restrict__ out, float clip) {
-    __shared__ uint32_t q_meta[kEncWarps][4][kQueueSlots];  // block index lo / hi, code so far, first open level
+    __shared__ uint32_t q_index[kEncWarps][2][kQueueSlots];  // block index lo / hi
     __shared__ int q_count[kEncWarps];
     auto emit = [&](int64_t b, uint32_t code, float s) {
         if (!RECON) {
@@ -257,24 +264,21 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
     __syncwarp();
     int count = 0;  // warp-uniform copy of q_count[warp] as of the last look
 
-    // Scaled row of block b (only called for b < n).
-    auto load_row = [&](int64_t b, float (&v)[8], float& s) {
-        e8::Row8<DT>::load(x, b, v);
-        s = load_scale<MODE>(scale, td, b);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = scale_in<MODE>(v[i], s);
-    };
     // Completes the last min(count, 32) queued blocks with all lanes busy.
     auto drain = [&]() {
         const int take = count < 32 ? count : 32;
         if (lane < take) {
             const int e = count - take + lane;
-            const int64_t b = (int64_t)(((uint64_t)q_meta[warp][1][e] << 32) | q_meta[warp][0][e]);
-            const uint32_t code = q_meta[warp][2][e];
-            const int start = (int)q_meta[warp][3][e];
-            float v[8], s;
-            load_row(b, v, s);
-            emit(b, e8::finish_block_q4(v, code, start), s);
+            const int64_t b = (int64_t)(((uint64_t)q_index[warp][1][e] << 32) | q_index[warp][0][e]);
+            float v[8];
+            e8::Row8<DT>::load(x, b, v);
+            const float s = load_scale<MODE>(scale, td, b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[i] = scale_in<MODE>(v[i], s);
+                if (SAT) v[i] = fminf(fmaxf(v[i], -kSaturate), kSaturate);  // NaN -> -kSaturate: finite, harmless
+            }
+            emit(b, e8::finish_block_q4(v, 0u, 0), s);
         }
         count -= take;
         __syncwarp();
@@ -285,15 +289,14 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
     const int64_t span = 32 * kRowsPerIter;
     const int64_t stride = (int64_t)gridDim.x * kEncWarps * span;
     for (int64_t base = ((int64_t)blockIdx.x * kEncWarps + warp) * span; base < n; base += stride) {
-        uint32_t code[kRowsPerIter];
-        int open_level[kRowsPerIter];  // first level still open; 2 = finished, 3 = no block (past the end)
-        float sc[kRowsPerIter];
-        bool any_open = false;
+        bool defer[kRowsPerIter];
+        bool any_defer = false;
         {
-            // All rows are requested first; the level-0 path then runs row after row in straight-line
-            // code, so the loads of the later rows and the FP32-heavy head of one row overlap the
-            // ALU-heavy tail of the previous one.  The rows are not kept beyond this scope.
+            // All rows are requested first; the tier then runs row after row in straight-line code, so
+            // the loads of the later rows overlap the arithmetic of the earlier ones.  The rows are not
+            // kept beyond this scope.
             float v[kRowsPerIter][8];
+            float sc[kRowsPerIter];
 #pragma unroll
             for (int j = 0; j < kRowsPerIter; ++j) {
                 const int64_t b = base + j * 32 + lane;
@@ -308,44 +311,35 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
             }
 #pragma unroll
             for (int j = 0; j < kRowsPerIter; ++j) {
-                const bool active = base + j * 32 + lane < n;
+                const int64_t b = base + j * 32 + lane;
                 float s1 = 0.0f;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     v[j][i] = scale_in<MODE>(v[j][i], sc[j]);
                     s1 += fabsf(v[j][i]);
                 }
-                // max |x_i| as a tree of three-input maxima (4 instructions instead of 8)
+                // max |x_i| as a tree of three-input maxima; a NaN is dropped by fmaxf but poisons s1
                 const float m0 = fmaxf(fmaxf(fabsf(v[j][0]), fabsf(v[j][1])), fabsf(v[j][2]));
                 const float m1 = fmaxf(fmaxf(fabsf(v[j][3]), fabsf(v[j][4])), fabsf(v[j][5]));
                 const float amax = fmaxf(fmaxf(m0, m1), fmaxf(fabsf(v[j][6]), fabsf(v[j][7])));
-                const bool finite = (s1 - s1) == 0.0f;
-                // top level: origin unless max|x| > 1.96 or sum|x| > 7.96 (the level sees x / 4); decided
-                // here so that only one predicate, not amax and s1, lives across the level-0 path
-                const bool top_open = !(amax <= 1.96f && s1 <= 7.96f);
-                code[j] = 0;
-                open_level[j] = 2;
-                if (!finite) {
-                    open_level[j] = 0;
-                } else if (!(amax <= 0.49f && s1 <= 1.99f)) {
-                    if (!e8::level_fast_q4<false>(v[j], amax, code[j])) open_level[j] = 0;
-                }
-                if (open_level[j] == 2 && top_open) open_level[j] = 1;
-                if (!active) open_level[j] = 3;  // past the end: neither stored nor queued
-                if (open_level[j] == 2) emit(base + j * 32 + lane, code[j], sc[j]);
-                any_open = any_open || open_level[j] < 2;
+                const bool pre = amax <= 1.96f && s1 <= 7.96f;       // top level is the origin, tier applicable
+                const bool origin = amax <= 0.49f && s1 <= 1.99f;    // this level is the origin too: code 0
+                uint32_t code;
+                const bool proven = e8::level_fast2_q4(v[j], code);
+                const bool done = origin || (pre && proven);
+                defer[j] = b < n && !done;
+                if (b < n && done) emit(b, origin ? 0u : code, sc[j]);
+                any_defer = any_defer || defer[j];
             }
         }
-        if (any_open) {  // rare: one branch per iteration keeps the queue code off the common path
+        if (any_defer) {  // rare: one branch per iteration keeps the queue code off the common path
 #pragma unroll
             for (int j = 0; j < kRowsPerIter; ++j) {
-                if (open_level[j] < 2) {
+                if (defer[j]) {
                     const int64_t b = base + j * 32 + lane;
                     const int pos = atomicAdd(&q_count[warp], 1);
-                    q_meta[warp][0][pos] = (uint32_t)b;
-                    q_meta[warp][1][pos] = (uint32_t)((uint64_t)b >> 32);
-                    q_meta[warp][2][pos] = code[j];
-                    q_meta[warp][3][pos] = (uint32_t)open_level[j];
+                    q_index[warp][0][pos] = (uint32_t)b;
+                    q_index[warp][1][pos] = (uint32_t)((uint64_t)b >> 32);
                 }
             }
         }
@@ -355,6 +349,194 @@ k_encode_q4m2_queued(const void* __restrict__ x, const float* __restrict__ scale
     }
     while (count > 0) drain();
 }
+
+// ---------------------------------------------------------------- encode-only production path
+// The codes-only encoder is two launches.  Measured on this part, ANY state carried across the loop of
+// the persistent kernel above (a queue length, a vote per iteration, a second loop) costs 10-25 % of
+// its time through register pressure at the 64-register budget, so the main kernel carries none: a
+// lane whose block the cheapest tier cannot prove stores a marker code (top level word non-zero, which
+// that tier never produces) and appends the block index to a list in scratch memory with one atomic
+// in a rare branch.  The fix-up kernel then finishes the listed blocks densely with the always-valid
+// tiers.  When more blocks are deferred than the list holds (an overloaded quantiser) the fix-up kernel
+// instead sweeps all codes for the marker and compacts the marked blocks warp by warp.
+constexpr uint32_t kDeferredMark = 0x80000000u;
+// The list is split into kDeferLists sub-lists (CTA i of the main kernel appends to sub-list i mod
+// kDeferLists), each with its own counter in its own 32-byte sector: appends do not contend for one
+// address (a single counter serialises: 2.7e5 appends took 0.4 ms).
+constexpr int kDeferLists = 256;
+constexpr int kCounterStride = 8;  // uint32 words between counters
+
+struct EncodeScratch {
+    uint32_t* ctrl;   // [kDeferLists * kCounterStride] counters, then [0] overflow flag, [1] fix-up CTAs finished
+    int64_t* list;    // kDeferLists sub-lists of `cap` entries
+    uint32_t cap;     // entries per sub-list
+};
+__device__ __forceinline__ uint32_t* scratch_tail(const EncodeScratch& s) { return s.ctrl + kDeferLists * kCounterStride; }
+
+template <int DT, int MODE>
+__global__ void __launch_bounds__(kThreads, 4)
+k_encode_q4m2_main(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
+                   uint32_t* __restrict__ codes, EncodeScratch sc_) {
+    __shared__ uint4 flip_rows[8];
+    if (threadIdx.x < 8) flip_rows[threadIdx.x] = e8::kFlipRows[threadIdx.x];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t span = 32 * kRowsPerIter;
+    const int64_t stride = (int64_t)gridDim.x * kEncWarps * span;
+    for (int64_t base = ((int64_t)blockIdx.x * kEncWarps + warp) * span; base < n; base += stride) {
+        float v[kRowsPerIter][8];
+        float sc[kRowsPerIter];
+#pragma unroll
+        for (int j = 0; j < kRowsPerIter; ++j) {
+            const int64_t b = base + j * 32 + lane;
+            sc[j] = 1.0f;
+            if (b < n) {
+                e8::Row8<DT>::load(x, b, v[j]);
+                sc[j] = load_scale<MODE>(scale, td, b);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[j][i] = 0.0f;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kRowsPerIter; ++j) {
+            const int64_t b = base + j * 32 + lane;
+            float s1 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[j][i] = scale_in<MODE>(v[j][i], sc[j]);
+                s1 += fabsf(v[j][i]);
+            }
+            // max |x_i| as a tree of three-input maxima; a NaN is dropped by fmaxf but poisons s1
+            const float m0 = fmaxf(fmaxf(fabsf(v[j][0]), fabsf(v[j][1])), fabsf(v[j][2]));
+            const float m1 = fmaxf(fmaxf(fabsf(v[j][3]), fabsf(v[j][4])), fabsf(v[j][5]));
+            const float amax = fmaxf(fmaxf(m0, m1), fmaxf(fabsf(v[j][6]), fabsf(v[j][7])));
+            const bool pre = amax <= 1.96f && s1 <= 7.96f;     // top level is the origin, tier applicable
+            const bool origin = amax <= 0.49f && s1 <= 1.99f;  // this level is the origin too: code 0
+            uint32_t code;
+            const bool proven = e8::level_fast2_q4(v[j], code, flip_rows);
+            const bool done = origin || (pre && proven);
+            if (b < n) {
+                if (done) {
+                    __stcs(codes + b, origin ? 0u : code);
+                } else {  // rare: mark the block and append it to this CTA's sub-list
+                    codes[b] = kDeferredMark;
+                    const uint32_t l = blockIdx.x % kDeferLists;
+                    const uint32_t pos = atomicAdd(sc_.ctrl + l * kCounterStride, 1u);
+                    if (pos < sc_.cap) sc_.list[(int64_t)l * sc_.cap + pos] = b;
+                    else *scratch_tail(sc_) = 1u;  // full: the fix-up kernel will sweep for the markers instead
+                }
+            }
+        }
+    }
+}
+
+// One level of a deferred block: the cheapest tier when it applies, then the exact-rounding tier, then the
+// literal search.  amax, s1: max and sum of |x_i|.
+__device__ __forceinline__ uint32_t level_any_q4(const float (&x)[8], float amax, float s1) {
+    uint32_t digits;
+    if (amax <= 1.96f && s1 <= 7.96f && e8::level_fast2_q4(x, digits)) return digits;
+    return e8::level_slow_q4(x, s1 == s1 && s1 - s1 == 0.0f ? amax : __int_as_float(0x7fc00000));
+}
+
+template <int DT, int MODE, bool SAT>
+__global__ void __launch_bounds__(kThreads)
+k_encode_q4m2_fix(const void* __restrict__ x, const float* __restrict__ scale, e8::TileDiv td, int64_t n,
+                  uint32_t* __restrict__ codes, EncodeScratch sc_) {
+    __shared__ uint32_t q_index[kEncWarps][2][64];
+    __shared__ uint32_t prefix[kDeferLists + 1];
+    const bool overflow = *reinterpret_cast<volatile uint32_t*>(scratch_tail(sc_)) != 0u;
+    auto finish = [&](int64_t b) {
+        float v[8];
+        e8::Row8<DT>::load(x, b, v);
+        const float s = load_scale<MODE>(scale, td, b);
+        float amax = 0.0f, s1 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[i] = scale_in<MODE>(v[i], s);
+            if (SAT) v[i] = fminf(fmaxf(v[i], -kSaturate), kSaturate);  // a NaN becomes -kSaturate: finite, harmless
+            amax = fmaxf(amax, fabsf(v[i]));
+            s1 += fabsf(v[i]);
+        }
+        uint32_t code = 0u;
+#pragma unroll 1
+        for (int m = 0; m < 2; ++m) {
+            const bool origin = amax <= 0.49f && s1 <= 1.99f;
+            if (!origin) code |= level_any_q4(v, amax, s1) << (16 * m);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], 0.25f);
+            amax *= 0.25f;
+            s1 *= 0.25f;
+        }
+        __stcs(codes + b, code);
+    };
+    if (!overflow) {
+        // every deferred block is in a sub-list.  Flatten them: exclusive prefix of the kDeferLists
+        // counters (one per thread), then one thread per entry across the whole grid, all lanes busy.
+        uint32_t cnt = *reinterpret_cast<volatile uint32_t*>(sc_.ctrl + threadIdx.x * kCounterStride);
+        prefix[threadIdx.x + 1] = cnt < sc_.cap ? cnt : sc_.cap;
+        if (threadIdx.x == 0) prefix[0] = 0u;
+        __syncthreads();
+        for (int o = 1; o < kDeferLists; o <<= 1) {  // Hillis-Steele inclusive scan over prefix[1..]
+            const uint32_t add = threadIdx.x + 1 > (unsigned)o ? prefix[threadIdx.x + 1 - o] : 0u;
+            __syncthreads();
+            prefix[threadIdx.x + 1] += add;
+            __syncthreads();
+        }
+        const uint32_t total = prefix[kDeferLists];
+        for (uint32_t f = blockIdx.x * kThreads + threadIdx.x; f < total; f += gridDim.x * kThreads) {
+            int lo = 0, hi = kDeferLists;  // largest l with prefix[l] <= f
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (prefix[mid] <= f) lo = mid; else hi = mid;
+            }
+            finish(sc_.list[(int64_t)lo * sc_.cap + (f - prefix[lo])]);
+        }
+    } else {
+        // a sub-list overflowed: sweep all codes for the marker, 32 marked blocks at a time per warp
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        int count = 0;
+        auto drain = [&](int take) {
+            if (lane < take) {
+                const int e = count - take + lane;
+                finish((int64_t)(((uint64_t)q_index[warp][1][e] << 32) | q_index[warp][0][e]));
+            }
+            count -= take;
+            __syncwarp();
+        };
+        const int64_t stride = (int64_t)gridDim.x * kEncWarps * 32;
+        for (int64_t base = ((int64_t)blockIdx.x * kEncWarps + warp) * 32; base < n; base += stride) {
+            const int64_t b = base + lane;
+            const bool marked = b < n && codes[b] == kDeferredMark;
+            const uint32_t bal = __ballot_sync(0xffffffffu, marked);
+            if (bal) {
+                if (marked) {
+                    const int pos = count + __popc(bal & ((1u << lane) - 1u));
+                    q_index[warp][0][pos] = (uint32_t)b;
+                    q_index[warp][1][pos] = (uint32_t)((uint64_t)b >> 32);
+                }
+                count += __popc(bal);
+                __syncwarp();
+                if (count >= 32) drain(32);
+            }
+        }
+        if (count > 0) drain(count);
+    }
+    // the last CTA to finish clears the counters and the flag for the next call on this scratch
+    __syncthreads();
+    __shared__ bool last;
+    if (threadIdx.x == 0) {
+        __threadfence();
+        last = atomicAdd(scratch_tail(sc_) + 1, 1u) == gridDim.x - 1u;
+    }
+    __syncthreads();
+    if (last) {
+        sc_.ctrl[threadIdx.x * kCounterStride] = 0u;
+        if (threadIdx.x == 0) { scratch_tail(sc_)[0] = 0u; scratch_tail(sc_)[1] = 0u; }
+        __threadfence();
+    }
+}
+static_assert(kDeferLists == kThreads, "the fix-up kernel scans one counter per thread");
 
 // Two blocks per thread (kThreads apart, so every access stays coalesced): both codes are
 // loaded before the first table lookup, which doubles the gathers in flight per thread.
@@ -510,6 +692,79 @@ const uint32_t* residual_table_q4_packed(cudaStream_t stream) {
 
 }  // namespace coset
 
+namespace {
+
+// Scratch of the two-launch encoder, one per (device, stream): calls on one stream are ordered, so they
+// may share it; the mutex keeps the two launches of one call together when several host threads use the
+// same stream.  Allocated on first use and when a larger tensor arrives (never inside a stream capture:
+// make the first call of a given size before capturing).
+struct ScratchSlot {
+    int device;
+    cudaStream_t stream;
+    EncodeScratch s;
+};
+std::mutex g_scratch_mu;
+std::vector<ScratchSlot> g_scratch;
+
+constexpr size_t kCtrlBytes = (size_t)(kDeferLists * kCounterStride + 8) * sizeof(uint32_t);
+
+int alloc_scratch(EncodeScratch* s, uint32_t cap, cudaStream_t st) {
+    *s = EncodeScratch{nullptr, nullptr, 0};
+    if (int e = check_cuda(cudaMalloc(&s->ctrl, kCtrlBytes), "cudaMalloc(encode scratch)")) return e;
+    if (int e = check_cuda(cudaMalloc(&s->list, (size_t)kDeferLists * cap * sizeof(int64_t)), "cudaMalloc(encode scratch)")) return e;
+    if (int e = check_cuda(cudaMemsetAsync(s->ctrl, 0, kCtrlBytes, st), "cudaMemsetAsync(encode scratch)")) return e;
+    s->cap = cap;
+    return 0;
+}
+
+int encode_scratch(cudaStream_t st, int64_t n_blocks, EncodeScratch* out) {
+    int dev = 0;
+    if (int e = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return e;
+    // room for one block in 32 deferred (the benchmark data defers one in 125), at least 64 per sub-list
+    const uint32_t want = (uint32_t)(n_blocks / 32 / kDeferLists) + 64u;
+    if ((uint64_t)want * kDeferLists >= 0xffffffffull) return fail(COSET_E_BADARG, "n_blocks too large");
+    for (auto& slot : g_scratch) {
+        if (slot.device == dev && slot.stream == st) {
+            if (slot.s.cap >= want) { *out = slot.s; return 0; }
+            // grow: earlier launches on this stream may still use the old buffers
+            if (int e = check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize(encode scratch)")) return e;
+            cudaFree(slot.s.ctrl);
+            cudaFree(slot.s.list);
+            if (int e = alloc_scratch(&slot.s, want, st)) return e;
+            *out = slot.s;
+            return 0;
+        }
+    }
+    ScratchSlot slot{dev, st, EncodeScratch{nullptr, nullptr, 0}};
+    if (int e = alloc_scratch(&slot.s, want, st)) return e;
+    g_scratch.push_back(slot);
+    *out = slot.s;
+    return 0;
+}
+
+template <int DT, int MODE>
+int launch_encode_q4m2(const void* x, const float* scale, e8::TileDiv td, int64_t n, uint32_t* codes, bool saturate,
+                       cudaStream_t st) {
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    EncodeScratch sc;
+    if (int e = encode_scratch(st, n, &sc)) return e;
+    const unsigned mgrid = encoder_grid(n);
+    k_encode_q4m2_main<DT, MODE><<<mgrid, kThreads, 0, st>>>(x, scale, td, n, codes, sc);
+    if (int e = check_launch("e8_encode (main)")) return e;
+    // the deferred blocks are few: a grid of four CTAs per SM shares them evenly (in sweep mode it strides
+    // over the whole tensor)
+    const int64_t need = (n + kThreads - 1) / kThreads;
+    const unsigned fgrid = (unsigned)(need < 4 * sm_count() ? (need < 1 ? 1 : need) : 4 * sm_count());
+    (void)mgrid;
+    if (saturate)
+        k_encode_q4m2_fix<DT, MODE, true><<<fgrid, kThreads, 0, st>>>(x, scale, td, n, codes, sc);
+    else
+        k_encode_q4m2_fix<DT, MODE, false><<<fgrid, kThreads, 0, st>>>(x, scale, td, n, codes, sc);
+    return check_launch("e8_encode (fix-up)");
+}
+
+}  // namespace
+
 #define DISPATCH_MODE(MODE_VAR, ...)                                   \
     switch (MODE_VAR) {                                                \
         case 0: { constexpr int MODE = 0; __VA_ARGS__; } break;         \
@@ -542,7 +797,9 @@ int coset_e8_encode(const void* x, int x_dtype, const float* scale, int scale_mo
     if (int e = check_common(x, codes, n_blocks, q, M)) return e;
     if (int e = check_scale(scale, scale_mode, blocks_per_tile)) return e;
     if (x_dtype != COSET_DTYPE_F32 && x_dtype != COSET_DTYPE_BF16) return fail(COSET_E_BADARG, "unknown x_dtype %d", x_dtype);
-    if (sem != COSET_SEM_CORE && sem != COSET_SEM_CORE_LITERAL) return fail(COSET_E_UNSUPPORTED, "semantics %d not available in this entry point", sem);
+    if (sem != COSET_SEM_CORE && sem != COSET_SEM_CORE_LITERAL && sem != COSET_SEM_CORE_SATURATE)
+        return fail(COSET_E_UNSUPPORTED, "semantics %d not available in this entry point", sem);
+    if (sem == COSET_SEM_CORE_SATURATE && !(q == 4 && M == 2)) return fail(COSET_E_UNSUPPORTED, "saturating encode needs q=4, M=2");
     if (n_blocks == 0) return 0;
     if (!aligned(x, 16) || !aligned(codes, 4)) return fail(COSET_E_ALIGN, "x must be 16-byte and codes 4-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
@@ -550,8 +807,13 @@ int coset_e8_encode(const void* x, int x_dtype, const float* scale, int scale_mo
     unsigned grid = grid_for(n_blocks);
     if (q == 4 && M == 2 && sem == COSET_SEM_CORE) {
         // persistent warps: at most kEncCtasPerSm CTAs per SM of grid (4 resident at a time)
-        unsigned qgrid = encoder_grid(n_blocks);
-        DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2_queued<DT, MODE, false, 0><<<qgrid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes, nullptr, nullptr, 0.0f))))
+        int rc = 0;
+        DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (rc = launch_encode_q4m2<DT, MODE>(x, scale, td, n_blocks, (uint32_t*)codes, false, st))))
+        return rc;
+    } else if (q == 4 && M == 2 && sem == COSET_SEM_CORE_SATURATE) {
+        int rc = 0;
+        DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (rc = launch_encode_q4m2<DT, MODE>(x, scale, td, n_blocks, (uint32_t*)codes, true, st))))
+        return rc;
     } else if (q == 4 && M == 2) {
         DISPATCH_DT(x_dtype, DT, DISPATCH_MODE(scale_mode, (k_encode_q4m2<DT, MODE, true><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes))))
     } else if (q <= 4) {
@@ -606,7 +868,7 @@ int coset_e8_quantize(const void* x, int x_dtype, const float* scale, int scale_
         const uint2* table = residual_table_q4(st);
         if (!table) return COSET_E_STATE;
         unsigned qgrid = encoder_grid(n_blocks);
-        DISPATCH_DT(x_dtype, DTI, DISPATCH_DT(out_dtype, DTO, DISPATCH_MODE(scale_mode, (k_encode_q4m2_queued<DTI, MODE, true, DTO><<<qgrid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes_out, table, out, clip)))))
+        DISPATCH_DT(x_dtype, DTI, DISPATCH_DT(out_dtype, DTO, DISPATCH_MODE(scale_mode, (k_encode_q4m2_queued<DTI, MODE, true, DTO, false><<<qgrid, kThreads, 0, st>>>(x, scale, td, n_blocks, (uint32_t*)codes_out, table, out, clip)))))
     } else if (q <= 4) {
         DISPATCH_DT(x_dtype, DTI, DISPATCH_DT(out_dtype, DTO, DISPATCH_MODE(scale_mode, (k_quantize_generic<DTI, DTO, MODE, 2><<<grid, kThreads, 0, st>>>(x, scale, td, n_blocks, q, M, clip, out, codes_out)))))
     } else {

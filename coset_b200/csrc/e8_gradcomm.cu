@@ -31,9 +31,12 @@ struct PeerStreams {
 template <int DT, bool PEERS>
 __global__ void __launch_bounds__(kThreads)
 k_decode_mean(const uint32_t* __restrict__ codes, PeerStreams peers, int world, int64_t n, int64_t stride, float divisor,
-              const uint2* __restrict__ table, void* __restrict__ out) {
+              const uint2* __restrict__ table, void* __restrict__ out, const int* __restrict__ status) {
     int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (b >= n) return;
+    // a bounded cross-rank wait before this launch gave up: the peers' streams are not known to be
+    // complete, so nothing is read or written
+    if (PEERS && status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
     // 16-bit lanes: acc[0] = coordinates (0,2), acc[1] = (1,3), acc[2] = (4,6), acc[3] = (5,7)
     uint32_t acc[4] = {0u, 0u, 0u, 0u};
     for (int r0 = 0; r0 < world; r0 += 4) {
@@ -80,7 +83,57 @@ k_decode_mean(const uint32_t* __restrict__ codes, PeerStreams peers, int world, 
     e8::Row8<DT>::store(out, b, o);
 }
 
+// Cross-rank "everyone has arrived" with a bound.  flags[r] is rank r's own array of `world` words
+// (peer / symmetric memory, mapped into this process); word s of it is written only by rank s.
+// Thread t tells rank t that this rank has reached `epoch` (one release store over NVLink into
+// flags[t][rank], after a system-scope fence that publishes everything this rank wrote before the
+// launch) and then polls its own flags[rank][t] until rank t has said the same.  Epochs only grow, so
+// the words are never cleared and a late reader of an old epoch passes at once.  The poll gives up
+// after timeout_ns of the global timer: it records that in *status and returns, and the kernels that
+// follow on the stream check *status before touching a peer's data.
+struct PeerFlags {
+    uint32_t* p[kMaxPeers];
+};
+
+__global__ void k_peer_signal_wait(PeerFlags flags, int world, int rank, uint32_t epoch, unsigned long long timeout_ns,
+                                   int* __restrict__ status) {
+    const int t = threadIdx.x;
+    if (t >= world) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.p[t] + rank), "r"(epoch) : "memory");
+    const uint32_t* mine = flags.p[rank] + t;
+    unsigned long long start;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+    for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if ((int32_t)(v - epoch) >= 0) break;
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (now - start > timeout_ns) {
+            if (status != nullptr) atomicExch(status, 1 + t);  // 1 + the rank that did not arrive
+            break;
+        }
+        __nanosleep(128);
+    }
+}
+
 }  // namespace
+
+extern "C" int coset_peer_signal_wait(void* const* rank_flags, int world, int rank, uint32_t epoch, int timeout_ms,
+                                      int* status, void* stream) {
+    if (world < 1 || world > kMaxPeers) return fail(COSET_E_BADARG, "world must be in 1..16");
+    if (rank < 0 || rank >= world) return fail(COSET_E_BADARG, "rank outside the world");
+    if (!rank_flags) return fail(COSET_E_BADARG, "null pointer");
+    PeerFlags f = {};
+    for (int r = 0; r < world; ++r) {
+        if (!rank_flags[r] || !aligned(rank_flags[r], 4)) return fail(COSET_E_BADARG, "flag array %d is null or misaligned", r);
+        f.p[r] = (uint32_t*)rank_flags[r];
+    }
+    const unsigned long long ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+    k_peer_signal_wait<<<1, 32, 0, (cudaStream_t)stream>>>(f, world, rank, epoch, ns, status);
+    return check_launch("peer_signal_wait");
+}
 
 extern "C" int coset_e8_decode_mean(const void* codes, int world, int64_t n_blocks, int64_t rank_stride_blocks,
                                     float scale, void* out, int out_dtype, void* stream) {
@@ -98,14 +151,14 @@ extern "C" int coset_e8_decode_mean(const void* codes, int world, int64_t n_bloc
     unsigned grid = (unsigned)((n_blocks + kThreads - 1) / kThreads);
     PeerStreams none = {};
     if (out_dtype == COSET_DTYPE_F32)
-        k_decode_mean<0, false><<<grid, kThreads, 0, st>>>((const uint32_t*)codes, none, world, n_blocks, rank_stride_blocks, divisor, table, out);
+        k_decode_mean<0, false><<<grid, kThreads, 0, st>>>((const uint32_t*)codes, none, world, n_blocks, rank_stride_blocks, divisor, table, out, nullptr);
     else
-        k_decode_mean<1, false><<<grid, kThreads, 0, st>>>((const uint32_t*)codes, none, world, n_blocks, rank_stride_blocks, divisor, table, out);
+        k_decode_mean<1, false><<<grid, kThreads, 0, st>>>((const uint32_t*)codes, none, world, n_blocks, rank_stride_blocks, divisor, table, out, nullptr);
     return check_launch("e8_decode_mean");
 }
 
 extern "C" int coset_e8_decode_mean_peers(const void* const* rank_codes, int world, int rank, int64_t n_blocks, float scale,
-                                          void* out, int out_dtype, void* stream) {
+                                          void* out, int out_dtype, const int* status, void* stream) {
     if (world < 1 || world > kMaxPeers) return fail(COSET_E_BADARG, "world must be in 1..16 for the peer-memory form");
     if (rank < 0 || rank >= world) return fail(COSET_E_BADARG, "rank outside the world");
     if (n_blocks < 0) return fail(COSET_E_BADARG, "n_blocks is negative");
@@ -126,8 +179,8 @@ extern "C" int coset_e8_decode_mean_peers(const void* const* rank_codes, int wor
     float divisor = scale * (float)world;
     unsigned grid = (unsigned)((n_blocks + kThreads - 1) / kThreads);
     if (out_dtype == COSET_DTYPE_F32)
-        k_decode_mean<0, true><<<grid, kThreads, 0, st>>>(nullptr, peers, world, n_blocks, 0, divisor, table, out);
+        k_decode_mean<0, true><<<grid, kThreads, 0, st>>>(nullptr, peers, world, n_blocks, 0, divisor, table, out, status);
     else
-        k_decode_mean<1, true><<<grid, kThreads, 0, st>>>(nullptr, peers, world, n_blocks, 0, divisor, table, out);
+        k_decode_mean<1, true><<<grid, kThreads, 0, st>>>(nullptr, peers, world, n_blocks, 0, divisor, table, out, status);
     return check_launch("e8_decode_mean_peers");
 }

@@ -10,7 +10,7 @@ prompts/design_instructions.md:104-110) but ships no code.  The exchange here is
 
 With transport="nccl" (default) each rank only reads its own memory; the collective is a plain
 all_gather_into_tensor.  With transport="peer" steps 3 and 4 are ONE kernel: every rank encodes into a
-buffer in symmetric memory, a device-side barrier of torch's symmetric-memory handle orders "all
+buffer in symmetric memory, the library's own bounded arrival (coset_peer_signal_wait) orders "all
 encoded", and the decode kernel reads the W code streams straight from the peers' memory over NVLink
 (plain loads, no multicast) while it decodes -- no gathered copy is written or re-read.  The
 arithmetic is fixed (exact sum of reconstructions, one float32 division), so every rank obtains
@@ -25,15 +25,32 @@ import torch.distributed as dist
 from . import _lib
 
 
+SATURATION = 3.9  # bound of a scaled coordinate under the saturating encode (COSET_SEM_CORE_SATURATE)
+
+
 class CudaCodec:
-    """The two device operations of the exchange, through the C ABI."""
+    """The two device operations of the exchange, through the C ABI.
+
+    saturate=True (default): every scaled value is clamped to +-SATURATION before it is quantised.
+    The q=4, M=2 code is periodic (it wraps modulo 16 E8), so without the clamp one gradient value
+    beyond the code's range would decode to an unrelated small number on every rank; with it the value
+    is clipped to SATURATION / scale, a bounded and visible error.  Blocks inside the range are coded
+    exactly as without the clamp."""
+
+    def __init__(self, saturate: bool = True):
+        self.saturate = bool(saturate)
+        self._scales = {}  # (device, scale) -> 1-element tensor: no allocation or host-to-device copy per call
 
     def encode(self, blocks: torch.Tensor, scale: float, out: torch.Tensor) -> torch.Tensor:
         n = blocks.shape[0]
-        s = torch.full((1,), float(scale), dtype=torch.float32, device=blocks.device)
+        key = (blocks.device, float(scale))
+        s = self._scales.get(key)
+        if s is None:
+            s = self._scales[key] = torch.full((1,), float(scale), dtype=torch.float32, device=blocks.device)
+        sem = _lib.SEM_CORE_SATURATE if self.saturate else _lib.SEM_CORE
         with torch.cuda.device(blocks.device):
             rc = _lib.lib().coset_e8_encode(_lib.ptr(blocks), _lib.dtype_code(blocks, "grad"), _lib.ptr(s),
-                                            _lib.SCALE_MUL_TILE, n, max(n, 1), 4, 2, _lib.SEM_CORE, _lib.ptr(out),
+                                            _lib.SCALE_MUL_TILE, n, max(n, 1), 4, 2, sem, _lib.ptr(out),
                                             _lib.stream())
         _lib.check(rc, "coset_e8_encode")
         return out
@@ -51,20 +68,33 @@ class E8GradientExchange:
 
     scale: shared multiplier applied before quantisation (the quantiser's step is 1/scale); it
     must be the same on every rank.  With gradients of standard deviation sigma, scale = 0.5/sigma
-    keeps the two-level code away from overload.
+    keeps the two-level code away from overload; values beyond SATURATION / scale are clipped there
+    (see CudaCodec), and `overloaded_fraction` reports how many blocks that concerns.
+    timeout_ms: bound of the cross-rank wait of the peer-memory transport (see coset_b200.peer).
     """
 
     def __init__(self, group: Optional[dist.ProcessGroup] = None, scale: float = 500.0, codec=None,
-                 transport: str = "nccl"):
+                 transport: str = "nccl", timeout_ms: int = 2000):
         if transport not in ("nccl", "peer"):
             raise ValueError("transport must be 'nccl' (all-gather, then decode) or 'peer' (decode from peer memory)")
         self.group = group
         self.scale = float(scale)
         self.codec = codec if codec is not None else CudaCodec()
         self.transport = transport
+        self.timeout_ms = int(timeout_ms)
         self._codes = None
         self._gathered = None
-        self._symm = {}  # n_blocks -> [buffer [2, n_blocks] int32, handle, parity]; one entry per bucket size
+        self._region = None      # one symmetric allocation [2, capacity] int32, grown (collectively) when a larger bucket arrives
+        self._capacity = 0
+        self._parity = 0
+        self._side = None        # stream of the asynchronous DDP hook
+        self.phase_events = None  # set to a list: a CUDA event is appended after encode, transfer and decode
+
+    def _mark(self):
+        if self.phase_events is not None and torch.cuda.is_available():
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.phase_events.append(ev)
 
     def _world(self):
         return dist.get_world_size(self.group) if dist.is_available() and dist.is_initialized() else 1
@@ -77,7 +107,8 @@ class E8GradientExchange:
         return self._codes, self._gathered
 
     def all_reduce_mean(self, flat: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """flat: 1-D float32 (or bfloat16) gradient on this rank -> 1-D average, same length."""
+        """flat: 1-D float32 (or bfloat16) gradient on this rank -> 1-D float32 average, same length.
+        out (float32, contiguous, same length) receives the result; it may be `flat` itself."""
         if flat.dim() != 1:
             raise ValueError("expected a flat 1-D gradient")
         if isinstance(self.codec, CudaCodec):
@@ -90,67 +121,106 @@ class E8GradientExchange:
         else:
             padded = flat.contiguous()
         world = self._world()
+        # the decode kernel writes straight into `out` when its layout allows (no padding, float32)
+        direct = (out is not None and n_blocks * 8 == n_values and out.dtype == torch.float32 and out.is_contiguous()
+                  and out.numel() == n_values and out.device == flat.device)
+        res = out.view(n_blocks, 8) if direct else torch.empty((n_blocks, 8), dtype=torch.float32, device=flat.device)
         if self.transport == "peer" and world > 1:
-            res = self._all_reduce_mean_peer(padded, n_blocks, world)
-            res = res.view(-1)[:n_values]
-            if out is not None:
-                out.copy_(res)
-                return out
-            return res
-        codes, gathered = self._buffers(n_blocks, world, flat.device)
-        self.codec.encode(padded.view(n_blocks, 8), self.scale, codes)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered.view(-1), codes, group=self.group)
+            self._all_reduce_mean_peer(padded, n_blocks, world, res)
         else:
-            gathered.view(-1).copy_(codes)
-        res = torch.empty((n_blocks, 8), dtype=torch.float32, device=flat.device)
-        self.codec.decode_mean(gathered, world, n_blocks, self.scale, res)
+            codes, gathered = self._buffers(n_blocks, world, flat.device)
+            self._mark()
+            self.codec.encode(padded.view(n_blocks, 8), self.scale, codes)
+            self._mark()
+            if world > 1:
+                dist.all_gather_into_tensor(gathered.view(-1), codes, group=self.group)
+            else:
+                gathered.view(-1).copy_(codes)
+            self._mark()
+            self.codec.decode_mean(gathered, world, n_blocks, self.scale, res)
+            self._mark()
+        if direct:
+            return out
         res = res.view(-1)[:n_values]
         if out is not None:
             out.copy_(res)
             return out
         return res
 
+    def overloaded_fraction(self, flat: torch.Tensor) -> float:
+        """Fraction of this rank's 8-value blocks whose scaled values leave the two-level code's range
+        (the overload test of ref/hnlq.py:341 through coset_e8_quant_stats).  Diagnostic: it reads the
+        tensor once more and synchronises; use it to pick `scale`, not on every step."""
+        from .core.e8.codecs import e8_quant_stats
+        n_values = flat.numel()
+        n_blocks = n_values // 8
+        if n_blocks == 0:
+            return 0.0
+        s = torch.full((1,), self.scale, dtype=torch.float32, device=flat.device)
+        stats = e8_quant_stats(flat[:n_blocks * 8].contiguous().view(n_blocks, 8), scale=s, scale_mode=_lib.SCALE_MUL_TILE,
+                               blocks_per_tile=n_blocks)
+        return float(stats["overloaded_blocks"]) / n_blocks
 
-def _peer_exchange(self, padded, n_blocks, world):
-    """Encode into this rank's half of a double-buffered symmetric allocation, barrier, decode from
-    every rank's buffer.  One barrier per call is enough: a rank overwrites half p only two calls
-    later, after the barrier of the call in between, which no rank passes before its own decode of
-    half p has been enqueued ahead of it on the same stream."""
-    import torch.distributed._symmetric_memory as symm
-    dev = padded.device
-    if n_blocks not in self._symm:  # collective: every rank sees the same sequence of sizes
-        buf = symm.empty(2, n_blocks, dtype=torch.int32, device=dev)
-        group = self.group if self.group is not None else dist.group.WORLD
-        hdl = symm.rendezvous(buf, group.group_name)
-        self._symm[n_blocks] = [buf, hdl, 0]
-    entry = self._symm[n_blocks]
-    buf, hdl, parity = entry
-    entry[2] = parity ^ 1
-    self.codec.encode(padded.view(n_blocks, 8), self.scale, buf[parity])
-    hdl.barrier(channel=parity)
-    res = torch.empty((n_blocks, 8), dtype=torch.float32, device=dev)
-    offset = parity * n_blocks * 4
-    ptrs = (ctypes.c_void_p * world)(*[int(p) + offset for p in hdl.buffer_ptrs])
-    with torch.cuda.device(dev):
-        rc = _lib.lib().coset_e8_decode_mean_peers(ctypes.cast(ptrs, ctypes.c_void_p), world, hdl.rank, n_blocks,
-                                                   float(self.scale), _lib.ptr(res), _lib.dtype_code(res, "out"),
-                                                   _lib.stream())
-    _lib.check(rc, "coset_e8_decode_mean_peers")
-    return res
+    def check(self):
+        """Raises if a bounded cross-rank wait of the peer-memory transport gave up (synchronises)."""
+        if self._region is not None:
+            self._region.check()
 
-
-E8GradientExchange._all_reduce_mean_peer = _peer_exchange
+    def _all_reduce_mean_peer(self, padded, n_blocks, world, res):
+        """Encode into one half of the symmetric allocation, bounded arrival, decode from every rank's
+        half.  One arrival per call is enough: a rank overwrites half p only two calls later, after the
+        arrival of the call in between, which no rank passes before its own decode of half p has been
+        enqueued ahead of it on the same stream."""
+        from .peer import SymmetricRegion
+        dev = padded.device
+        if n_blocks > self._capacity:  # collective: every rank sees the same sequence of sizes
+            if self._region is not None:  # peers may still be reading the old allocation
+                torch.cuda.synchronize(dev)
+                dist.barrier(group=self.group)
+            self._capacity = n_blocks
+            self._region = SymmetricRegion(2 * n_blocks * 4, dev, self.group, self.timeout_ms)
+            self._parity = 0
+        region, parity = self._region, self._parity
+        self._parity ^= 1
+        half = region.data(torch.int32)[parity * self._capacity: parity * self._capacity + n_blocks]
+        self.codec.encode(padded.view(n_blocks, 8), self.scale, half)
+        region.arrive()
+        ptrs = region.pointers(parity * self._capacity * 4)
+        with torch.cuda.device(dev):
+            rc = _lib.lib().coset_e8_decode_mean_peers(ctypes.cast(ptrs, ctypes.c_void_p), world, region.rank, n_blocks,
+                                                       float(self.scale), _lib.ptr(res), _lib.dtype_code(res, "out"),
+                                                       _lib.ptr(region.status), _lib.stream())
+        _lib.check(rc, "coset_e8_decode_mean_peers")
+        return res
 
 
 def e8_allreduce_hook(state: E8GradientExchange, bucket) -> torch.futures.Future[torch.Tensor]:
     """torch DDP communication hook: `ddp.register_comm_hook(E8GradientExchange(group), e8_allreduce_hook)`.
 
-    The bucket's flat gradient is replaced by its E8-quantised average."""
+    The bucket's flat gradient is replaced by its E8-quantised average.  On a CUDA device the exchange
+    runs on a side stream of `state` and the returned future completes with it, so the exchange of one
+    bucket overlaps the backward pass that fills the next; buckets are exchanged in order on that one
+    stream, which is also what makes the reuse of `state`'s buffers safe."""
     buf = bucket.buffer()
-    avg = state.all_reduce_mean(buf.float() if buf.dtype not in (torch.float32, torch.bfloat16) else buf)
-    fut = torch.futures.Future()
-    fut.set_result(avg.to(buf.dtype))
+    if not buf.is_cuda:
+        avg = state.all_reduce_mean(buf.float() if buf.dtype not in (torch.float32, torch.bfloat16) else buf)
+        fut = torch.futures.Future()
+        fut.set_result(avg.to(buf.dtype))
+        return fut
+    if state._side is None:
+        state._side = torch.cuda.Stream(device=buf.device)
+    side = state._side
+    side.wait_stream(torch.cuda.current_stream(buf.device))
+    fut = torch.futures.Future(devices=[buf.device])
+    with torch.cuda.stream(side):
+        src = buf.float() if buf.dtype not in (torch.float32, torch.bfloat16) else buf
+        if buf.dtype == torch.float32:
+            state.all_reduce_mean(src, out=buf)  # decoded straight into the bucket
+            result = buf
+        else:
+            result = state.all_reduce_mean(src).to(buf.dtype)
+        buf.record_stream(side)
+        fut.set_result(result)  # records the side stream's work; consumers wait for it on their own stream
     return fut
 
 

@@ -167,16 +167,17 @@ class ColumnParallelE8CodeLinear(nn.Module):
     The codes never cross the link; at T = 1 the all-gather is latency-bound.
 
     transport="peer" (few tokens, T <= local.small_t_max): the product kernel writes every result row
-    straight into the result buffer of EVERY rank (symmetric memory, plain stores over NVLink), a
-    device-side barrier of the symmetric-memory handle follows, and no all-gather is issued."""
+    straight into the result buffer of EVERY rank (symmetric memory, plain stores over NVLink), the
+    library's bounded cross-rank arrival follows (coset_b200.peer), and no all-gather is issued."""
 
-    def __init__(self, local: E8CodeLinear, out_features: int, group=None, transport: str = "nccl"):
+    def __init__(self, local: E8CodeLinear, out_features: int, group=None, transport: str = "nccl", timeout_ms: int = 2000):
         super().__init__()
         import torch.distributed as dist
         if transport not in ("nccl", "peer"):
             raise ValueError("transport must be 'nccl' or 'peer'")
         self.transport = transport
-        self._symm = {}  # T -> [buffer [2, T, out_features] float32, handle, parity]
+        self.timeout_ms = int(timeout_ms)
+        self._region, self._cap_tokens, self._parity = None, 0, 0  # symmetric result buffer [2, tokens, out_features]
         self.local = local
         self.group = group
         self.world = dist.get_world_size(group)
@@ -206,18 +207,21 @@ class ColumnParallelE8CodeLinear(nn.Module):
     def _forward_peer(self, x2: torch.Tensor) -> torch.Tensor:
         import ctypes
         import torch.distributed as dist
-        import torch.distributed._symmetric_memory as symm
+        from .peer import SymmetricRegion
         T = x2.shape[0]
-        if T not in self._symm:  # collective: every rank sees the same sequence of token counts
-            buf = symm.empty(2, T, self.out_features, dtype=torch.float32, device=x2.device)
-            group = self.group if self.group is not None else dist.group.WORLD
-            self._symm[T] = [buf, symm.rendezvous(buf, group.group_name), 0]
-        entry = self._symm[T]
-        buf, hdl, parity = entry
-        entry[2] = parity ^ 1
+        if T > self._cap_tokens:  # collective: every rank sees the same sequence of token counts
+            if self._region is not None:  # peers may still be writing into the old allocation
+                torch.cuda.synchronize(x2.device)
+                dist.barrier(group=self.group)
+            self._cap_tokens = T
+            self._region = SymmetricRegion(2 * T * self.out_features * 4, x2.device, self.group, self.timeout_ms)
+            self._parity = 0
+        region, parity = self._region, self._parity
+        self._parity ^= 1
+        half_elems = self._cap_tokens * self.out_features
         lo, _ = out_feature_shard(self.out_features, self.world, self.rank)
-        offset = (parity * T * self.out_features + lo) * 4  # this rank's columns inside half `parity`
-        targets = (ctypes.c_void_p * self.world)(*[int(p) + offset for p in hdl.buffer_ptrs])
+        offset = (parity * half_elems + lo) * 4  # this rank's columns inside half `parity`
+        targets = region.pointers(offset)
         loc = self.local
         x2 = x2.contiguous()
         bias32 = loc.bias.to(torch.float32).contiguous() if loc.bias is not None else None
@@ -227,9 +231,15 @@ class ColumnParallelE8CodeLinear(nn.Module):
                 _lib.ptr(x2), _lib.dtype_code(x2, "x"), x2.stride(0), T, _lib.ptr(bias32) if bias32 is not None else None,
                 ctypes.cast(targets, ctypes.c_void_p), self.world, self.out_features, _lib.stream())
         _lib.check(rc, "coset_e8_vlut_gemv_scatter")
-        hdl.barrier(channel=parity)  # all ranks have written their columns into this rank's buffer
-        # the half is written again two calls from now, after the barrier of the call in between
-        return buf[parity].clone()
+        region.arrive()  # bounded: all ranks have written their columns into this rank's buffer
+        # the half is written again two calls from now, after the arrival of the call in between
+        mine = region.data(torch.float32)[parity * half_elems: parity * half_elems + T * self.out_features]
+        return mine.view(T, self.out_features).clone()
+
+    def check(self):
+        """Raises if a bounded cross-rank wait of the peer-store path gave up (synchronises)."""
+        if self._region is not None:
+            self._region.check()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist

@@ -58,6 +58,11 @@ extern "C" {
 #define COSET_SEM_CORE 0
 #define COSET_SEM_REF 1
 #define COSET_SEM_CORE_LITERAL 2 /* same results as CORE, every block through the op-by-op search (validation) */
+#define COSET_SEM_CORE_SATURATE 3 /* CORE after clamping every scaled coordinate to +-3.9 (q=4, M=2 encode only): the
+                                     two-level code then never wraps around (its top level stays the origin), so an
+                                     outlier costs a bounded clipping error instead of an unrelated reconstruction;
+                                     identical to CORE for blocks with max|scaled x| <= 3.9.  No counterpart in the
+                                     reference, whose codec wraps silently (coset/core/e8/codecs.py:63-89). */
 
 #define COSET_E_BADARG (-1)   /* null pointer, negative size, unknown enum */
 #define COSET_E_UNSUPPORTED (-2) /* q / M / dtype combination not implemented */
@@ -81,6 +86,11 @@ int coset_e8_projection(const float* x, int64_t n_blocks, float* y, void* stream
  * e8_encode (coset/core/e8/codecs.py:17-89): scale, then M levels of
  * encode_coords(projection(x / q^m)) (coset/core/base.py:134-154), written as packed codes.
  * x: [n_blocks, 8] of x_dtype (16-byte aligned).  codes: packed, 4-byte aligned.
+  * For q = 4, M = 2 the call is two launches (main kernel + a short fix-up kernel for the blocks the
+ * cheapest tier cannot prove) and uses a few MB of library-owned scratch per (device, stream), allocated
+ * on the first call and when a larger tensor arrives: make the first call of a given size before a
+ * stream capture begins.  Calls on one stream share the scratch (they are ordered); concurrent calls
+ * on different streams have their own.
  */
 int coset_e8_encode(const void* x, int x_dtype, const float* scale, int scale_mode,
                     int64_t n_blocks, int64_t blocks_per_tile, int q, int M, int sem,
@@ -173,11 +183,27 @@ int coset_e8_decode_mean(const void* codes, int world, int64_t n_blocks, int64_t
  * points at rank r's own code buffer, mapped into this process (peer / symmetric memory); the kernel
  * reads the peers' streams with plain loads over NVLink while it decodes, starting at stream `rank`.
  * The caller orders "every rank has finished encoding" before this call and "every rank has finished
- * reading" before the buffers are overwritten (a device-side barrier of its communication library).
+ * reading" before the buffers are overwritten (coset_peer_signal_wait below, enqueued between the
+ * encode and this call).  status (device int, may be NULL): when not NULL and non-zero at run time --
+ * a wait before this launch gave up -- the kernel reads and writes nothing.
  * world <= 16.  Same arithmetic, bit-identical result.
  */
 int coset_e8_decode_mean_peers(const void* const* rank_codes, int world, int rank, int64_t n_blocks,
-                               float scale, void* out, int out_dtype, void* stream);
+                               float scale, void* out, int out_dtype, const int* status, void* stream);
+/*
+ * Bounded cross-rank arrival for the peer-memory paths (the exchange planned at
+ * prompts/design_instructions.md:104-110 has no counterpart code in the reference).
+ * rank_flags[r] (host array of `world` device pointers) is rank r's array of `world` uint32 words in
+ * peer / symmetric memory, zero before first use; word s of every array is written only by rank s.
+ * The one-CTA kernel publishes everything this rank wrote earlier on the stream, stores `epoch` into
+ * word `rank` of every rank's array and waits until its own array holds an epoch >= `epoch` from every
+ * rank.  Epochs must grow by one per call (wrap-around is handled).  The wait is bounded: after
+ * timeout_ms (<= 0: 2000 ms) it stores 1 + (the first rank found missing) into *status (device int, may be
+ * NULL) and returns, so a rank that died leaves its peers' streams and contexts usable.
+ * world <= 16.  Every rank runs on its own GPU: two ranks that wait for each other must never share one.
+ */
+int coset_peer_signal_wait(void* const* rank_flags, int world, int rank, uint32_t epoch, int timeout_ms,
+                           int* status, void* stream);
 
 /*
  * Code-domain ("vLUT") product for inference, small token counts:

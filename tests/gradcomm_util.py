@@ -15,12 +15,22 @@ def cpu_decode_mean(codes_per_rank, scale):
     return (total / div).astype(np.float32)
 
 
+SATURATION = np.float32(3.9)  # coset_b200.gradcomm.SATURATION / COSET_SEM_CORE_SATURATE
+
+
+def oracle_encode_saturating(blocks, scale):
+    """The exchange's encode step on the CPU: x * scale in float32, every value clamped to
+    +-SATURATION, then the reference codec without further scaling -> float digits [n, 2, 8]."""
+    xs = (np.asarray(blocks, np.float32) * np.float32(scale)).astype(np.float32)
+    xs = np.minimum(np.maximum(xs, -SATURATION), SATURATION)
+    return O.encode(xs)
+
+
 class OracleCodec:
     """Drop-in for coset_b200.gradcomm.CudaCodec on CPU tensors (tests of the host logic only)."""
 
     def encode(self, blocks, scale, out):
-        n = blocks.shape[0]
-        digits = O.encode(blocks.numpy(), beta=np.array([scale], np.float32), scale_mode=2, blocks_per_tile=max(n, 1))
+        digits = oracle_encode_saturating(blocks.numpy(), scale)
         out.copy_(torch.from_numpy(O.pack_q4(digits).view(np.int32)))
         return out
 

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from conftest import bits
-from gradcomm_util import cpu_decode_mean
+from gradcomm_util import cpu_decode_mean, oracle_encode_saturating
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -27,12 +27,44 @@ def test_decode_mean_matches_cpu_recipe(world):
         g = torch.Generator().manual_seed(1000 + r)
         grad = (torch.randn(n, 8, generator=g) * 1e-3)
         codec.encode(grad.cuda(), scale, gathered[r])
-        d = O.encode(grad.numpy(), beta=np.array([scale], np.float32), scale_mode=2, blocks_per_tile=n)
+        d = oracle_encode_saturating(grad.numpy(), scale)
         assert np.array_equal(gathered[r].cpu().numpy().view(np.uint32), O.pack_q4(d))
         digits.append(d)
     out = torch.empty((n, 8), device="cuda")
     codec.decode_mean(gathered, world, n, scale, out)
     assert np.array_equal(bits(out.cpu().numpy()), bits(cpu_decode_mean(digits, scale)))
+
+
+def test_outlier_block_is_clipped_not_wrapped():
+    """One gradient value far outside the two-level code's range: the saturating encode clips it to
+    3.9 / scale (bit for bit the CPU recipe with the clamp); the plain codec wraps it to an unrelated
+    small value, which is what the exchange must never do silently."""
+    from coset_b200.gradcomm import CudaCodec, E8GradientExchange, SATURATION
+    from gradcomm_util import oracle_encode_saturating
+    n, scale = 4096, 500.0
+    g = torch.Generator().manual_seed(7)
+    grad = torch.randn(n, 8, generator=g) * 1e-3
+    grad[17, 3] = 0.25        # 125 lattice units: far beyond the range of the code
+    grad[900] = -0.05         # a whole block at -25 units
+    grad[901, 0] = float("inf")
+    codes = torch.empty(n, dtype=torch.int32, device="cuda")
+    CudaCodec().encode(grad.cuda(), scale, codes)
+    want = oracle_encode_saturating(grad.numpy(), scale)
+    assert np.array_equal(codes.cpu().numpy().view(np.uint32), O.pack_q4(want))
+    out = torch.empty((n, 8), device="cuda")
+    CudaCodec().decode_mean(codes.view(1, n), 1, n, scale, out)
+    out = out.cpu()
+    assert abs(float(out[17, 3]) - SATURATION / scale) <= 1.0 / scale      # clipped, within a lattice unit
+    assert float((out[900] + SATURATION / scale).abs().max()) <= 1.5 / scale
+    assert bool(torch.isfinite(out).all())
+    # the plain codec wraps the same value around
+    plain = torch.empty(n, dtype=torch.int32, device="cuda")
+    CudaCodec(saturate=False).encode(grad.nan_to_num(posinf=0.0).cuda(), scale, plain)
+    out2 = torch.empty((n, 8), device="cuda")
+    CudaCodec().decode_mean(plain.view(1, n), 1, n, scale, out2)
+    assert abs(float(out2[17, 3].cpu()) - 0.25) > 0.2
+    frac = E8GradientExchange(scale=scale).overloaded_fraction(grad.nan_to_num(posinf=0.0).reshape(-1).cuda())
+    assert 2 / n <= frac <= 8 / n
 
 
 def test_single_gpu_exchange_roundtrip():
@@ -44,6 +76,54 @@ def test_single_gpu_exchange_roundtrip():
     # farther coset (reference semantics), so the check is on the median and on the total
     assert float((avg - g).abs().median()) < 0.5 / 500.0
     assert float((avg - g).norm() / g.norm()) < 1.0
+
+
+def test_bounded_arrival_gives_up_and_guards_the_decode():
+    """The cross-rank wait is bounded.  One GPU plays rank 0 of a two-rank world whose "peer" is a
+    plain device array that nothing ever writes: the wait must run out, report the missing rank in
+    the status word and leave the context usable; the decode that follows must then touch nothing.
+    Once the peer's word is set the same calls pass and decode as the all-gather form does."""
+    import ctypes
+    from coset_b200 import _lib
+    from coset_b200.gradcomm import CudaCodec
+    L = _lib.lib()
+    n, scale = 3000, 500.0
+    flags = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(2)]
+    fptr = (ctypes.c_void_p * 2)(*[f.data_ptr() for f in flags])
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    codec = CudaCodec()
+    gathered = torch.empty((2, n), dtype=torch.int32, device="cuda")
+    for r in range(2):
+        g = torch.Generator().manual_seed(50 + r)
+        codec.encode((torch.randn(n, 8, generator=g) * 1e-3).cuda(), scale, gathered[r])
+    cptr = (ctypes.c_void_p * 2)(*[gathered[r].data_ptr() for r in range(2)])
+    out = torch.full((n, 8), -7.0, device="cuda")
+
+    def arrive(epoch):
+        rc = L.coset_peer_signal_wait(ctypes.cast(fptr, ctypes.c_void_p), 2, 0, epoch, 50, _lib.ptr(status), _lib.stream())
+        assert rc == 0, L.coset_last_error_string()
+
+    def decode():
+        rc = L.coset_e8_decode_mean_peers(ctypes.cast(cptr, ctypes.c_void_p), 2, 0, n, scale, _lib.ptr(out), 0,
+                                          _lib.ptr(status), _lib.stream())
+        assert rc == 0, L.coset_last_error_string()
+
+    arrive(1)
+    decode()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 2                      # 1 + the rank that never arrived
+    assert int(flags[0][0]) == 1 and int(flags[1][0]) == 1  # this rank did signal itself and its peer
+    assert bool((out == -7.0).all())                    # the guarded decode wrote nothing
+    status.zero_()
+    flags[0][1] = 2                                     # "rank 1 has reached epoch 2"
+    arrive(2)
+    decode()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    want = torch.empty((n, 8), device="cuda")
+    codec.decode_mean(gathered, 2, n, scale, want)
+    assert torch.equal(out, want)
+    assert L.coset_peer_signal_wait(ctypes.cast(fptr, ctypes.c_void_p), 17, 0, 1, 50, None, None) < 0
 
 
 WORKER = r'''
@@ -154,11 +234,12 @@ via_peer = E8GradientExchange(scale=500.0, transport="peer")
 n_values = 8 * 50000 + 3
 for it in range(6):  # several calls in a row: both halves of the double buffer are reused; two sizes alternate
     g = torch.Generator().manual_seed(1000 * it + rank)
-    grad = (torch.randn(n_values if it % 2 == 0 else 8 * 777, generator=g) * 1e-3).cuda()
+    grad = (torch.randn(n_values if it % 2 == 1 else 8 * 777, generator=g) * 1e-3).cuda()  # the second call grows the symmetric allocation
     a = via_nccl.all_reduce_mean(grad)
     b = via_peer.all_reduce_mean(grad)
     torch.cuda.synchronize()
     assert torch.equal(a, b), f"transports differ at call {it}"
+via_peer.check()
 dist.barrier()
 if rank == 0:
     print("PEER_OK")
