@@ -431,17 +431,36 @@ class HNLQLinearQAT(nn.Module):
             summary["weight_comparison"] = self.compare_weights()
         return summary
 
-    def export_quantized(self):
+    def export_quantized(self, packed: bool = False):
         """Dense fake-quantised weights + metadata, as the reference returns them
-        (coset/core/layers.py:620-650)."""
+        (coset/core/layers.py:620-650).
+
+        packed=True (q = 4 with the E8 quantiser only): instead of the dense float weights, the packed
+        two-level E8 codes (int32 [out_features, in_features / 8], 4 bytes per 8 weights), the scales
+        beta, blocks_per_tile, the bias and metadata including weight_clip_value -- everything
+        coset_b200.vlut.E8CodeLinear.from_exported needs to compute clamp(decode(codes) / beta) @ x."""
         with torch.no_grad():
-            W_q = self._quantize_weights()
             metadata = {"lattice_type": self.lattice_type, "q": self.q, "M": self.M, "Delta0": self.Delta0,
                         "tiling": self.tiling, "block_size": self.block_size,
                         "quantize_activations": self.quantize_activations}
             if self.quantize_activations and self.actq is not None:
                 metadata.update({"act_bit_width": self.actq.bit_width, "act_alpha": self.actq.alpha.item()})
-            return {"weight": W_q, "bias": self.bias, "metadata": metadata}
+            if not packed:
+                return {"weight": self._quantize_weights(), "bias": self.bias, "metadata": metadata}
+            if not (self._fused and self.q == 4):
+                raise ValueError("packed export stores q=4 two-level E8 codes; this layer uses "
+                                 f"lattice {self.lattice_type}, q={self.q}")
+            from .e8.codecs import e8_encode_packed
+            _lib.require_float32(self.weight, "weight")
+            beta = self._beta().detach().to(torch.float32).contiguous()
+            bpt = self.blocks_per_row if self.tiling == "row" else 1
+            codes = e8_encode_packed(self.weight.detach().contiguous().view(-1, 8), 4, 2, scale=beta.view(-1),
+                                     scale_mode=_lib.SCALE_MUL_TILE, blocks_per_tile=bpt)
+            metadata.update({"packed_M": 2, "weight_clip_value": float(self.weight_clip_value),
+                             "code_layout": "uint32 per block: level m digit j at bit 16 m + 2 j"})
+            return {"codes": codes.view(torch.int32).view(self.out_features, self.blocks_per_row), "beta": beta,
+                    "blocks_per_tile": bpt, "bias": self.bias.detach().clone() if self.bias is not None else None,
+                    "metadata": metadata}
 
     def extra_repr(self):
         return (f"in_features={self.in_features}, out_features={self.out_features}, "

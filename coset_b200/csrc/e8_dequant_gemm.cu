@@ -118,7 +118,7 @@ template <int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ beta, e8::TileDiv td, int N, int K,
                const __grid_constant__ CUtensorMap x_map, int T, const float* __restrict__ bias,
-               const uint2* __restrict__ table, float* __restrict__ y, int64_t ldy, int* __restrict__ status) {
+               const uint2* __restrict__ table, float* __restrict__ y, int64_t ldy, int* __restrict__ status, float clip) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;           // tiles need 1024-byte alignment for the 128B swizzle
@@ -220,8 +220,13 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
                 float half_inv = MODE == 2 ? __fdividef(0.5f, beta_c[j]) : 0.5f;
                 float v2[8];
                 e8::twice_from_entries(lo_c[j], hi_c[j], v2);
-                uint4 v = make_uint4(pack_bf16x2(v2[0] * half_inv, v2[1] * half_inv), pack_bf16x2(v2[2] * half_inv, v2[3] * half_inv),
-                                     pack_bf16x2(v2[4] * half_inv, v2[5] * half_inv), pack_bf16x2(v2[6] * half_inv, v2[7] * half_inv));
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v2[i] *= half_inv;
+                if (clip > 0.0f) {  // the training layer's clamp(decode / beta, +-clip), coset/core/layers.py:463
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v2[i] = fminf(fmaxf(v2[i], -clip), clip);
+                }
+                uint4 v = make_uint4(pack_bf16x2(v2[0], v2[1]), pack_bf16x2(v2[2], v2[3]), pack_bf16x2(v2[4], v2[5]), pack_bf16x2(v2[6], v2[7]));
                 *reinterpret_cast<uint4*>(b_gen + slot_off[j]) = v;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
@@ -320,7 +325,7 @@ int make_x_map(CUtensorMap* map, const void* x, int K, int T, int64_t ldx) {
 
 extern "C" int coset_e8_dequant_gemm(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
                                      const void* x_bf16, int64_t ldx, int T, const float* bias, float* y, int64_t ldy,
-                                     int* status, void* stream) {
+                                     float clip, int* status, void* stream) {
     if (n_out < 0 || n_in < 0 || T < 0 || (n_in % BK) != 0) return fail(COSET_E_BADARG, "bad shape (n_in must be a multiple of 64)");
     if (n_out == 0 || T == 0) return 0;
     if (!codes || !x_bf16 || !y) return fail(COSET_E_BADARG, "null pointer");
@@ -337,10 +342,10 @@ extern "C" int coset_e8_dequant_gemm(const void* codes, const float* beta, int64
     if (grid.y > 65535) return fail(COSET_E_UNSUPPORTED, "T too large");
     if (beta) {
         if (int e = check_cuda(cudaFuncSetAttribute(k_dequant_gemm<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), "cudaFuncSetAttribute")) return e;
-        k_dequant_gemm<2><<<grid, THREADS, SMEM_BYTES, st>>>((const uint32_t*)codes, beta, td, n_out, n_in, x_map, T, bias, table, y, ldy, status);
+        k_dequant_gemm<2><<<grid, THREADS, SMEM_BYTES, st>>>((const uint32_t*)codes, beta, td, n_out, n_in, x_map, T, bias, table, y, ldy, status, clip > 0.0f ? clip : 0.0f);
     } else {
         if (int e = check_cuda(cudaFuncSetAttribute(k_dequant_gemm<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), "cudaFuncSetAttribute")) return e;
-        k_dequant_gemm<0><<<grid, THREADS, SMEM_BYTES, st>>>((const uint32_t*)codes, beta, td, n_out, n_in, x_map, T, bias, table, y, ldy, status);
+        k_dequant_gemm<0><<<grid, THREADS, SMEM_BYTES, st>>>((const uint32_t*)codes, beta, td, n_out, n_in, x_map, T, bias, table, y, ldy, status, clip > 0.0f ? clip : 0.0f);
     }
     return check_launch("e8_dequant_gemm");
 }

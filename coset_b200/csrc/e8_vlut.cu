@@ -50,11 +50,13 @@ struct Targets {
     int n;
 };
 
-template <int TT, int XDT, int MODE>
+// CLIP: the weights are clamp(decode / beta, +-clip) as the training layer applies it
+// (coset/core/layers.py:463); the clamp acts on single weights, so every weight is scaled first.
+template <int TT, int XDT, int MODE, bool CLIP>
 __global__ void __launch_bounds__(kWarps * 32)
 k_vlut_gemv(const uint32_t* __restrict__ codes, const float* __restrict__ beta, e8::TileDiv td, int n_out, int kb,
             const void* __restrict__ x, int64_t ldx, int T, const float* __restrict__ bias,
-            const uint2* __restrict__ table, Targets out, int64_t ldy) {
+            const uint2* __restrict__ table, Targets out, int64_t ldy, float clip) {
     int row = blockIdx.x * kWarps + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
     int t0 = blockIdx.y * TT;
@@ -101,18 +103,18 @@ k_vlut_gemv(const uint32_t* __restrict__ codes, const float* __restrict__ beta, 
                 float v2[8];
                 e8::twice_from_entries(t_lo[j], t_hi[j], v2);
                 const float half_inv = MODE == COSET_SCALE_MUL_TILE ? __fdividef(0.5f, s_c[j]) : 0.5f;
-                if (TT >= 4) {  // many tokens share the block: scale the 8 weights once instead
+                if (TT >= 4 || CLIP) {  // many tokens share the block: scale the 8 weights once instead
                     float w[8];
                     e8::scale_twice<MODE == COSET_SCALE_MUL_TILE ? 2 : 0>(v2, s_c[j], w);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) v2[i] = w[i];
+                    for (int i = 0; i < 8; ++i) v2[i] = CLIP ? fminf(fmaxf(w[i], -clip), clip) : w[i];
                 }
 #pragma unroll
                 for (int t = 0; t < TT; ++t) {
                     if (t0 + t < T) {
                         float xv[8];
                         load_x8<XDT>(x, (int64_t)(t0 + t) * ldx + (int64_t)blk * 8, xv);
-                        if (TT >= 4) {
+                        if (TT >= 4 || CLIP) {
                             float a = acc[t];
 #pragma unroll
                             for (int i = 0; i < 8; ++i) a = __fmaf_rn(v2[i], xv[i], a);
@@ -140,10 +142,11 @@ k_vlut_gemv(const uint32_t* __restrict__ codes, const float* __restrict__ beta, 
     }
 }
 
-template <int XDT, int MODE>
+template <int XDT, int MODE, bool CLIP>
 void launch_gemv(int tt, dim3 grid, cudaStream_t st, const uint32_t* codes, const float* beta, e8::TileDiv td, int n_out,
-                 int kb, const void* x, int64_t ldx, int T, const float* bias, const uint2* table, const Targets& y, int64_t ldy) {
-#define GEMV_CASE(TT) k_vlut_gemv<TT, XDT, MODE><<<grid, kWarps * 32, 0, st>>>(codes, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy)
+                 int kb, const void* x, int64_t ldx, int T, const float* bias, const uint2* table, const Targets& y, int64_t ldy,
+                 float clip) {
+#define GEMV_CASE(TT) k_vlut_gemv<TT, XDT, MODE, CLIP><<<grid, kWarps * 32, 0, st>>>(codes, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy, clip)
     switch (tt) {
         case 1: GEMV_CASE(1); break;
         case 2: GEMV_CASE(2); break;
@@ -157,7 +160,8 @@ void launch_gemv(int tt, dim3 grid, cudaStream_t st, const uint32_t* codes, cons
 }  // namespace
 
 static int vlut_gemv_impl(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in, const void* x,
-                          int x_dtype, int64_t ldx, int T, const float* bias, const Targets& y, int64_t ldy, void* stream) {
+                          int x_dtype, int64_t ldx, int T, const float* bias, const Targets& y, int64_t ldy, float clip,
+                          void* stream) {
     if (n_out < 0 || n_in < 0 || T < 0 || (n_in % 8) != 0) return fail(COSET_E_BADARG, "bad shape (n_in must be a multiple of 8)");
     if (n_out == 0 || T == 0) return 0;
     if (!codes || !x) return fail(COSET_E_BADARG, "null pointer");
@@ -176,29 +180,32 @@ static int vlut_gemv_impl(const void* codes, const float* beta, int64_t blocks_p
     dim3 grid((n_out + kWarps - 1) / kWarps, (T + tt - 1) / tt);
     if (grid.y > 65535) return fail(COSET_E_UNSUPPORTED, "T too large for the small-T kernel");
     const uint32_t* c = (const uint32_t*)codes;
+    if (!(clip == clip)) return fail(COSET_E_BADARG, "clip is not a number");
+#define GEMV_LAUNCH(XDT, MODE)                                                                                              \
+    if (clip > 0.0f) launch_gemv<XDT, MODE, true>(tt, grid, st, c, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy, clip); \
+    else launch_gemv<XDT, MODE, false>(tt, grid, st, c, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy, 0.0f)
     if (x_dtype == COSET_DTYPE_F32) {
-        if (beta) launch_gemv<0, 2>(tt, grid, st, c, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy);
-        else launch_gemv<0, 0>(tt, grid, st, c, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy);
+        if (beta) { GEMV_LAUNCH(0, 2); } else { GEMV_LAUNCH(0, 0); }
     } else {
-        if (beta) launch_gemv<1, 2>(tt, grid, st, c, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy);
-        else launch_gemv<1, 0>(tt, grid, st, c, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy);
+        if (beta) { GEMV_LAUNCH(1, 2); } else { GEMV_LAUNCH(1, 0); }
     }
+#undef GEMV_LAUNCH
     return check_launch("e8_vlut_gemv");
 }
 
 extern "C" int coset_e8_vlut_gemv(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
                                   const void* x, int x_dtype, int64_t ldx, int T, const float* bias, float* y,
-                                  int64_t ldy, void* stream) {
+                                  int64_t ldy, float clip, void* stream) {
     if (!y && n_out > 0 && T > 0) return fail(COSET_E_BADARG, "null pointer");
     Targets t = {};
     t.y[0] = y;
     t.n = 1;
-    return vlut_gemv_impl(codes, beta, blocks_per_tile, n_out, n_in, x, x_dtype, ldx, T, bias, t, ldy, stream);
+    return vlut_gemv_impl(codes, beta, blocks_per_tile, n_out, n_in, x, x_dtype, ldx, T, bias, t, ldy, clip, stream);
 }
 
 extern "C" int coset_e8_vlut_gemv_scatter(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
                                           const void* x, int x_dtype, int64_t ldx, int T, const float* bias,
-                                          float* const* y_targets, int n_targets, int64_t ldy, void* stream) {
+                                          float* const* y_targets, int n_targets, int64_t ldy, float clip, void* stream) {
     if (n_targets < 1 || n_targets > kMaxTargets || !y_targets) return fail(COSET_E_BADARG, "need 1..16 result buffers");
     Targets t = {};
     for (int k = 0; k < n_targets; ++k) {
@@ -206,5 +213,5 @@ extern "C" int coset_e8_vlut_gemv_scatter(const void* codes, const float* beta, 
         t.y[k] = y_targets[k];
     }
     t.n = n_targets;
-    return vlut_gemv_impl(codes, beta, blocks_per_tile, n_out, n_in, x, x_dtype, ldx, T, bias, t, ldy, stream);
+    return vlut_gemv_impl(codes, beta, blocks_per_tile, n_out, n_in, x, x_dtype, ldx, T, bias, t, ldy, clip, stream);
 }

@@ -21,8 +21,9 @@ from .core.e8.codecs import e8_decode_packed, e8_encode_packed
 
 
 def e8_vlut_matmul(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_per_tile: int, x: torch.Tensor,
-                   bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y = x @ Wq.T + bias with Wq = decode(codes) / beta; codes int32 [n_out, n_in / 8]; x [T, n_in]."""
+                   bias: Optional[torch.Tensor] = None, clip: float = 0.0) -> torch.Tensor:
+    """y = x @ Wq.T + bias with Wq = decode(codes) / beta (clamped to +-clip when clip > 0);
+    codes int32 [n_out, n_in / 8]; x [T, n_in]."""
     _lib.require_cuda(codes, "codes")
     _lib.require_cuda(x, "x")
     if codes.dtype != torch.int32 or codes.dim() != 2 or not codes.is_contiguous():
@@ -39,13 +40,13 @@ def e8_vlut_matmul(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_per
         rc = _lib.lib().coset_e8_vlut_gemv(_lib.ptr(codes), _lib.ptr(b) if b is not None else None, int(blocks_per_tile),
                                            n_out, kb * 8, _lib.ptr(x), _lib.dtype_code(x, "x"), x.stride(0), T,
                                            _lib.ptr(bias32) if bias32 is not None else None, _lib.ptr(y), y.stride(0),
-                                           _lib.stream())
+                                           float(clip), _lib.stream())
     _lib.check(rc, "coset_e8_vlut_gemv")
     return y
 
 
 def e8_dequant_gemm(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_per_tile: int, x: torch.Tensor,
-                    bias: Optional[torch.Tensor] = None, check: bool = False) -> torch.Tensor:
+                    bias: Optional[torch.Tensor] = None, check: bool = False, clip: float = 0.0) -> torch.Tensor:
     """Same product as e8_vlut_matmul for many tokens, on the tcgen05 tensor cores: weight tiles are
     decoded to bf16 in shared memory and never written to HBM.  x: bf16 [T, n_in], n_in % 64 == 0.
     check=True synchronises and raises if a bounded barrier wait expired inside the kernel."""
@@ -68,7 +69,7 @@ def e8_dequant_gemm(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_pe
         rc = _lib.lib().coset_e8_dequant_gemm(_lib.ptr(codes), _lib.ptr(b) if b is not None else None,
                                               int(blocks_per_tile), n_out, kb * 8, _lib.ptr(x), x.stride(0), T,
                                               _lib.ptr(bias32) if bias32 is not None else None, _lib.ptr(y),
-                                              y.stride(0), _lib.ptr(status), _lib.stream())
+                                              y.stride(0), float(clip), _lib.ptr(status), _lib.stream())
     _lib.check(rc, "coset_e8_dequant_gemm")
     if check and int(status.item()) != 0:
         raise RuntimeError("coset_e8_dequant_gemm: a barrier wait expired inside the kernel; the result is invalid")
@@ -76,14 +77,19 @@ def e8_dequant_gemm(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_pe
 
 
 class E8CodeLinear(nn.Module):
-    """Linear layer that owns E8 codes + scales instead of a dense weight (inference only)."""
+    """Linear layer that owns E8 codes + scales instead of a dense weight (inference only).
+
+    Its state_dict is self-describing (codes, beta, bias, blocks_per_tile, weight_clip_value), so a
+    layer can be rebuilt from a checkpoint alone with `E8CodeLinear.from_state_dict`.
+    weight_clip_value > 0: the weights are clamp(decode(codes) / beta, +-clip), the clamp the training
+    layer applies after de-scaling (coset/core/layers.py:463); 0 disables it."""
 
     def __init__(self, codes: torch.Tensor, beta: torch.Tensor, blocks_per_tile: int,
-                 bias: Optional[torch.Tensor] = None, small_t_max: int = 64, large_t_path: str = "cublas"):
+                 bias: Optional[torch.Tensor] = None, small_t_max: int = 64, large_t_path: str = "cublas",
+                 weight_clip_value: float = 0.0):
         super().__init__()
         self.out_features, kb = codes.shape
         self.in_features = kb * 8
-        self.blocks_per_tile = int(blocks_per_tile)
         self.small_t_max = small_t_max
         if large_t_path not in ("cublas", "tcgen05"):
             raise ValueError("large_t_path must be 'cublas' (dequantise once + library GEMM) or 'tcgen05' (fused kernel)")
@@ -91,7 +97,17 @@ class E8CodeLinear(nn.Module):
         self.register_buffer("codes", codes.contiguous())
         self.register_buffer("beta", beta.to(torch.float32).contiguous().view(-1))
         self.register_buffer("bias", bias.detach().clone() if bias is not None else None)
-        self._dense = None  # bf16 copy, built on first large-T call
+        self.register_buffer("blocks_per_tile_t", torch.tensor(int(blocks_per_tile), dtype=torch.int64))
+        self.register_buffer("weight_clip_value_t", torch.tensor(float(weight_clip_value), dtype=torch.float32))
+        self.blocks_per_tile = int(blocks_per_tile)
+        self.weight_clip_value = float(weight_clip_value)
+        self._dense, self._dense_key = None, None  # bf16 copy for the library GEMM, rebuilt when codes / scales change
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+        self.blocks_per_tile = int(self.blocks_per_tile_t.item())
+        self.weight_clip_value = float(self.weight_clip_value_t.item())
+        self._dense, self._dense_key = None, None
 
     @classmethod
     def from_weight(cls, weight: torch.Tensor, beta: torch.Tensor, blocks_per_tile: int, bias=None, **kw):
@@ -107,38 +123,57 @@ class E8CodeLinear(nn.Module):
 
     @classmethod
     def from_qat_layer(cls, layer, **kw):
-        """Export of a trained HNLQLinearQAT (q must be 4): codes, scales and bias.
+        """Export of a trained HNLQLinearQAT (q must be 4): codes, scales, bias and the layer's
+        weight_clip_value, so that this layer computes what the trained one computes."""
+        return cls.from_exported(layer.export_quantized(packed=True), **kw)
 
-        Note: the exported layer omits the training-time clamp to +-weight_clip_value."""
-        if layer.q != 4:
+    @classmethod
+    def from_exported(cls, exported: dict, **kw):
+        """Rebuild from HNLQLinearQAT.export_quantized(packed=True)."""
+        meta = exported["metadata"]
+        if meta.get("q") != 4 or meta.get("packed_M", 2) != 2:
             raise ValueError("E8CodeLinear stores q=4, M=2 codes")
-        with torch.no_grad():
-            beta = layer._beta().detach()
-            bpt = layer.blocks_per_row if layer.tiling == "row" else 1
-            return cls.from_weight(layer.weight.detach(), beta, bpt, layer.bias, **kw)
+        kw.setdefault("weight_clip_value", meta.get("weight_clip_value", 0.0))
+        return cls(exported["codes"], exported["beta"], int(exported["blocks_per_tile"]), exported.get("bias"), **kw)
+
+    @classmethod
+    def from_state_dict(cls, state_dict: dict, prefix: str = "", **kw):
+        """Rebuild from a checkpoint of this class alone (no codes in hand)."""
+        g = lambda k: state_dict[prefix + k]
+        bias = state_dict.get(prefix + "bias")
+        kw.setdefault("weight_clip_value", float(g("weight_clip_value_t")))
+        return cls(g("codes"), g("beta"), int(g("blocks_per_tile_t")), bias, **kw)
 
     def dense_weight(self, dtype=torch.float32) -> torch.Tensor:
-        """Wq = decode(codes) / beta as a dense [n_out, n_in] tensor."""
+        """Wq = clamp(decode(codes) / beta) as a dense [n_out, n_in] tensor."""
         w = e8_decode_packed(self.codes.view(-1), 4, 2, scale=self.beta, scale_mode=_lib.SCALE_MUL_TILE,
-                             blocks_per_tile=self.blocks_per_tile, dtype=dtype)
+                             blocks_per_tile=self.blocks_per_tile, dtype=torch.float32 if self.weight_clip_value > 0 else dtype)
+        if self.weight_clip_value > 0:
+            w = w.clamp_(-self.weight_clip_value, self.weight_clip_value).to(dtype)
         return w.view(self.out_features, self.in_features)
+
+    def _dense_bf16(self):
+        key = (self.codes._version, self.beta._version, self.codes.data_ptr(), self.beta.data_ptr(), self.codes.device,
+               self.weight_clip_value, self.blocks_per_tile)
+        if self._dense is None or self._dense_key != key:
+            self._dense, self._dense_key = self.dense_weight(torch.bfloat16), key
+        return self._dense
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.in_features)
+        clip = self.weight_clip_value
         if x2.shape[0] <= self.small_t_max:
-            y = e8_vlut_matmul(self.codes, self.beta, self.blocks_per_tile, x2, self.bias)
+            y = e8_vlut_matmul(self.codes, self.beta, self.blocks_per_tile, x2, self.bias, clip)
             y = y.to(x.dtype) if x.dtype != torch.float32 else y
         else:
             if x2.dtype == torch.float32:
                 y = torch.nn.functional.linear(x2, self.dense_weight(torch.float32), self.bias)
             elif self.large_t_path == "tcgen05" and x2.dtype == torch.bfloat16 and self.in_features % 64 == 0:
-                y = e8_dequant_gemm(self.codes, self.beta, self.blocks_per_tile, x2, self.bias).to(x2.dtype)
+                y = e8_dequant_gemm(self.codes, self.beta, self.blocks_per_tile, x2, self.bias, clip=clip).to(x2.dtype)
             else:
-                if self._dense is None:
-                    self._dense = self.dense_weight(torch.bfloat16)
                 b = self.bias.to(x2.dtype) if self.bias is not None else None
-                y = torch.nn.functional.linear(x2, self._dense.to(x2.dtype), b)
+                y = torch.nn.functional.linear(x2, self._dense_bf16().to(x2.dtype), b)
         return y.reshape(*lead, self.out_features)
 
 
@@ -229,7 +264,8 @@ class ColumnParallelE8CodeLinear(nn.Module):
             rc = _lib.lib().coset_e8_vlut_gemv_scatter(
                 _lib.ptr(loc.codes), _lib.ptr(loc.beta), loc.blocks_per_tile, loc.out_features, loc.in_features,
                 _lib.ptr(x2), _lib.dtype_code(x2, "x"), x2.stride(0), T, _lib.ptr(bias32) if bias32 is not None else None,
-                ctypes.cast(targets, ctypes.c_void_p), self.world, self.out_features, _lib.stream())
+                ctypes.cast(targets, ctypes.c_void_p), self.world, self.out_features, float(loc.weight_clip_value),
+                _lib.stream())
         _lib.check(rc, "coset_e8_vlut_gemv_scatter")
         region.arrive()  # bounded: all ranks have written their columns into this rank's buffer
         # the half is written again two calls from now, after the arrival of the call in between

@@ -214,11 +214,13 @@ int coset_peer_signal_wait(void* const* rank_flags, int world, int rank, uint32_
  *   beta  : per-tile scale in the layer convention (may be NULL = no scale);
  *           blocks_per_tile = n_in/8 for one scale per row, 1 for one per block
  *   x     : [T, ldx] float32 or bf16 (rows 16-byte aligned);  y: [T, ldy] float32
+ *   clip  : > 0: every weight is clamp(decode / beta, +-clip), the layer's weight_clip_value
+ *           (coset/core/layers.py:463), so that an exported layer computes what the trained one did; 0: none
  * Memory-bound on the code stream; meant for T <= ~64 (larger T: dequantise + tensor cores).
  */
 int coset_e8_vlut_gemv(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
                        const void* x, int x_dtype, int64_t ldx, int T, const float* bias, float* y,
-                       int64_t ldy, void* stream);
+                       int64_t ldy, float clip, void* stream);
 /*
  * The same product with the result rows written into SEVERAL buffers at once: y_targets (host array of
  * n_targets <= 16 device pointers) are the places of this rank's output-feature slice in the result
@@ -229,7 +231,7 @@ int coset_e8_vlut_gemv(const void* codes, const float* beta, int64_t blocks_per_
 int coset_e8_vlut_gemv_scatter(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out,
                                int n_in, const void* x, int x_dtype, int64_t ldx, int T,
                                const float* bias, float* const* y_targets, int n_targets, int64_t ldy,
-                               void* stream);
+                               float clip, void* stream);
 
 /*
  * Quantisation statistics of the q=4, M=2 codec over a tensor (one pass, deterministic):
@@ -330,7 +332,7 @@ int coset_lattice_babai(const float* x, int64_t n_blocks, int dim, const float* 
  */
 int coset_e8_dequant_gemm(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
                           const void* x_bf16, int64_t ldx, int T, const float* bias, float* y, int64_t ldy,
-                          int* status, void* stream);
+                          float clip /* as in coset_e8_vlut_gemv; 0 = none */, int* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -68,15 +68,41 @@ def test_literal_scale_gives_zero_output():
 
 
 def test_export_from_trained_layer():
+    """Default weight_clip_value (2.0) with N(0, 20) weights: the clamp is active on most weights and the
+    exported layer must still compute what the trained layer computes."""
     from coset_b200.core.e8 import create_e8_hnlq_linear
     from coset_b200.vlut import E8CodeLinear
-    layer = create_e8_hnlq_linear(128, 64, device="cuda", init_kwargs={"std": 20.0}, weight_clip_value=1e9)
+    layer = create_e8_hnlq_linear(128, 64, device="cuda", init_kwargs={"std": 20.0})
     lin = E8CodeLinear.from_qat_layer(layer)
+    assert lin.weight_clip_value == 2.0
     x = torch.randn(5, 128, device="cuda")
     with torch.no_grad():
         assert rel(lin(x).cpu().numpy(), layer(x).cpu().numpy()) < 1e-5
     with pytest.raises(ValueError):
         E8CodeLinear.from_weight(torch.zeros(4, 12, device="cuda"), torch.ones(4, device="cuda"), 1)
+
+
+@pytest.mark.parametrize("tiling", ["block", "row"])
+def test_weight_clip_in_every_kernel(tiling):
+    """clamp(decode / beta, +-clip) with a clip that cuts about a third of the weights, against the CPU
+    restatement: few-token kernel (float32 and bf16 activations), library path and fused tcgen05 kernel."""
+    from coset_b200.vlut import E8CodeLinear, e8_dequant_gemm
+    W, beta, bpt, digits, w_hat = make(256, 512, tiling)
+    clip = 0.03
+    w_clip = np.clip(w_hat, -clip, clip)
+    assert 0.1 < (np.abs(w_hat) > clip).mean() < 0.6
+    bias = torch.randn(256)
+    lin = E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt, bias.cuda(), weight_clip_value=clip)
+    assert np.array_equal(lin.dense_weight().cpu().numpy(), w_clip)
+    for T in (1, 3, 16, 40):
+        x = torch.randn(T, 512)
+        want = x.double().numpy() @ w_clip.astype(np.float64).T + bias.double().numpy()
+        assert rel(lin(x.cuda()).cpu().numpy(), want) < 1e-5, T
+    xb = torch.randn(300, 512).to(torch.bfloat16)
+    want = xb.float().numpy().astype(np.float64) @ w_clip.astype(np.float64).T + bias.double().numpy()
+    assert rel(lin(xb.cuda()).float().cpu().numpy(), want) < 1e-2
+    got = e8_dequant_gemm(lin.codes, lin.beta, bpt, xb.cuda(), lin.bias, check=True, clip=clip)
+    assert rel(got.cpu().numpy(), want) < 1e-2
 
 
 @pytest.mark.parametrize("T,n_out,n_in,tiling", [(128, 128, 64, "block"), (256, 256, 512, "block"), (300, 200, 1024, "row"), (1100, 384, 256, "block"),
