@@ -96,6 +96,54 @@ class _E8FakeQuant(torch.autograd.Function):
         return grad_w, (grad_beta.view(beta_shape) if need_beta else None), None, None, None, None
 
 
+class _E8LayerFakeQuant(torch.autograd.Function):
+    """The layer's whole weight path in one call each way: the per-tile scale
+    beta = beta_min + sigmoid(theta) * (beta_max - beta_min) is computed on the device
+    (coset_e8_layer_fake_quant_fwd), and the backward call returns dL/dW and dL/dtheta directly
+    (coset_e8_layer_fake_quant_bwd), so no small torch kernels sit around the two CUDA kernels."""
+
+    @staticmethod
+    def forward(ctx, weight, theta, beta_min, beta_range, blocks_per_tile, q, clip, out_dtype):
+        _lib.require_float32(weight, "weight")
+        _lib.require_cuda(weight, "weight")
+        w = weight.contiguous()
+        th = theta.detach().to(torch.float32).contiguous().view(-1)
+        n_blocks = w.numel() // 8
+        lib = _lib.lib()
+        code_bytes = lib.coset_e8_code_bytes(q, 2)
+        if code_bytes == 0:
+            raise ValueError(f"unsupported q={q} for the fused E8 weight quantiser (2 <= q <= 16)")
+        codes = torch.empty((n_blocks, code_bytes), dtype=torch.uint8, device=w.device)
+        out = torch.empty(w.shape, dtype=out_dtype, device=w.device)
+        beta = torch.empty_like(th)
+        with torch.cuda.device(w.device):
+            rc = lib.coset_e8_layer_fake_quant_fwd(_lib.ptr(w), _lib.ptr(th), _lib.ptr(beta_min), _lib.ptr(beta_range), n_blocks,
+                                                   blocks_per_tile, q, float(clip), _lib.ptr(out), _lib.dtype_code(out, "out"),
+                                                   _lib.ptr(codes), _lib.ptr(beta), _lib.stream())
+        _lib.check(rc, "coset_e8_layer_fake_quant_fwd")
+        ctx.save_for_backward(w, th, beta, beta_range, codes)
+        ctx.meta = (blocks_per_tile, q, float(clip), theta.shape)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        w, th, beta, beta_range, codes = ctx.saved_tensors
+        blocks_per_tile, q, clip, theta_shape = ctx.meta
+        g = grad_out.contiguous()
+        if g.dtype not in (torch.float32, torch.bfloat16):
+            g = g.float()
+        grad_w = torch.empty_like(w)
+        need_theta = ctx.needs_input_grad[1]
+        grad_theta = torch.empty_like(th) if need_theta else None
+        with torch.cuda.device(w.device):
+            rc = _lib.lib().coset_e8_layer_fake_quant_bwd(_lib.ptr(g), _lib.dtype_code(g, "grad"), _lib.ptr(w), _lib.ptr(codes),
+                                                          _lib.ptr(beta), _lib.ptr(th), _lib.ptr(beta_range), w.numel() // 8,
+                                                          blocks_per_tile, q, clip, _lib.ptr(grad_w), _lib.ptr(grad_theta),
+                                                          _lib.stream())
+        _lib.check(rc, "coset_e8_layer_fake_quant_bwd")
+        return grad_w, (grad_theta.view(theta_shape) if need_theta else None), None, None, None, None, None, None
+
+
 def e8_fake_quantize(weight, beta, blocks_per_tile, q=4, clip=2.0, out_dtype=torch.float32):
     """Differentiable fused weight quantiser used by HNLQLinearQAT (see _E8FakeQuant)."""
     return _E8FakeQuant.apply(weight, beta, int(blocks_per_tile), int(q), float(clip), out_dtype)
@@ -258,7 +306,22 @@ class HNLQLinearQAT(nn.Module):
 
     def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
         super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
-        self._step_host = int(self.step_count.item())
+        self._step_host = int(self._buffers["step_count"].item())
+
+    def _sync_step_count(self):
+        self._buffers["step_count"].fill_(self._step_host)
+
+    def _save_to_state_dict(self, destination, prefix, keep_vars):
+        self._sync_step_count()
+        super()._save_to_state_dict(destination, prefix, keep_vars)
+
+    def __getattr__(self, name):
+        if name == "step_count" and "step_count" in self.__dict__.get("_buffers", {}):
+            # reading the buffer brings it up to date with the host-side counter
+            buf = self.__dict__["_buffers"]["step_count"]
+            buf.fill_(self.__dict__.get("_step_host", 0))
+            return buf
+        return super().__getattr__(name)
 
     # ------------------------------------------------------------------ scale bounds
     def _gather_stats(self, W_blocks):
@@ -296,8 +359,22 @@ class HNLQLinearQAT(nn.Module):
         return self._bounds_cache[0], self._bounds_cache[1]
 
     def _beta(self):
+        """beta = beta_min + sigmoid(theta) * (beta_max - beta_min) per tile (coset/core/layers.py:415-417),
+        differentiable w.r.t. theta.  For CUDA parameters the forward value comes from the library's own
+        kernel (coset_layer_beta), the same arithmetic the fused weight path uses, so that the scales a
+        caller reads here are bit for bit the ones the weights were quantised with."""
         beta_min, _ = self._bounds()
-        return beta_min + torch.sigmoid(self.theta_beta) * self._bounds_cache[2]
+        rng = self._bounds_cache[2]
+        th = self.theta_beta
+        soft = beta_min + torch.sigmoid(th) * rng
+        if not th.is_cuda or th.dtype != torch.float32:
+            return soft
+        exact = torch.empty_like(beta_min)
+        with torch.cuda.device(th.device):
+            rc = _lib.lib().coset_layer_beta(_lib.ptr(th.detach().contiguous()), _lib.ptr(beta_min), _lib.ptr(rng), th.numel(),
+                                             _lib.ptr(exact), _lib.stream())
+        _lib.check(rc, "coset_layer_beta")
+        return exact + (soft - soft.detach())  # value of the kernel, gradient of the torch expression
 
     # ------------------------------------------------------------------ quantised weights
     def _quantize_weights(self, out_dtype=torch.float32):
@@ -306,22 +383,25 @@ class HNLQLinearQAT(nn.Module):
             if self.enable_diagnostics:
                 self._weight_history.append(W.detach().clone())
             return W
+        # the step counter lives on the host; the `step_count` buffer is brought up to date when it is
+        # read (state_dict, int(layer.step_count) through the property below) -- one launch less per step
         self._step_host += 1
-        self.step_count += 1
         if self._step_host % self.stat_update_interval == 0:
+            self._sync_step_count()
             self._gather_stats(W.detach().view(self.out_features, self.blocks_per_row, self.block_size))
-        beta = self._beta()  # [tiles], differentiable w.r.t. theta_beta
         bpt = self.blocks_per_row if self.tiling == "row" else 1
         if self._fused and W.is_cuda:
-            W_q = e8_fake_quantize(W, beta, bpt, self.q, self.weight_clip_value, out_dtype)
+            beta_min, _ = self._bounds()
+            W_q = _E8LayerFakeQuant.apply(W, self.theta_beta, beta_min, self._bounds_cache[2], bpt, int(self.q),
+                                          float(self.weight_clip_value), out_dtype)
         elif self._fused_d4 and W.is_cuda:
             from .d4.layers import d4_fake_quantize
-            W_q = d4_fake_quantize(W, beta, bpt, self.weight_clip_value, out_dtype)
+            W_q = d4_fake_quantize(W, self._beta(), bpt, self.weight_clip_value, out_dtype)
         elif self._fused or self._fused_d4:
             raise ValueError("HNLQLinearQAT with the E8 / D4 quantiser needs its parameters on a CUDA device "
                              "(coset_b200 has no CPU path); call .to('cuda')")
         else:
-            W_q = self._quantize_weights_opwise(W, beta)
+            W_q = self._quantize_weights_opwise(W, self._beta())
         if self.enable_diagnostics:
             self._weight_history.append(W.detach().clone())
             self._quantization_errors.append(torch.norm(W - W_q.float()).item())
@@ -340,7 +420,8 @@ class HNLQLinearQAT(nn.Module):
         W_q = self._quantize_weights(torch.bfloat16 if low else torch.float32)
         bias = self.bias
         if low:
-            W_q = W_q.to(torch.bfloat16)
+            if W_q.dtype != torch.bfloat16:  # warm-up (dense weights) or a user-supplied quantiser
+                W_q = W_q.to(torch.bfloat16)
             bias = bias.to(torch.bfloat16) if bias is not None else None
         x = F.linear(x, W_q, bias)
         if self.quantize_activations and self.actq is not None:

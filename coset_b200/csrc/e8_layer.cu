@@ -104,7 +104,69 @@ k_bwd_row_tiles(const void* __restrict__ g, const float* __restrict__ w, const v
     if (lane == 0 && dbeta) dbeta[tile] = acc;
 }
 
+// Per-tile scale of the layer (coset/core/layers.py:415-417):
+//   beta = beta_min + sigmoid(theta) * (beta_max - beta_min),   sigmoid(t) = 1 / (1 + exp(-t))
+// and its backward: d theta = (d beta * range) * (1 - s) * s, the product torch autograd forms for
+// mul followed by sigmoid.
+__device__ __forceinline__ float sigmoidf_exact(float t) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-t))); }
+
+__global__ void __launch_bounds__(kThreads)
+k_layer_beta(const float* __restrict__ theta, const float* __restrict__ bmin, const float* __restrict__ brange, int64_t tiles,
+             float* __restrict__ beta) {
+    int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= tiles) return;
+    beta[i] = __fadd_rn(__ldg(bmin + i), __fmul_rn(sigmoidf_exact(__ldg(theta + i)), __ldg(brange + i)));
+}
+
+__global__ void __launch_bounds__(kThreads)
+k_layer_dtheta(const float* __restrict__ theta, const float* __restrict__ brange, int64_t tiles, float* __restrict__ grad) {
+    int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= tiles) return;
+    const float s = sigmoidf_exact(__ldg(theta + i));
+    const float t = __fmul_rn(grad[i], __ldg(brange + i));
+    grad[i] = __fmul_rn(__fmul_rn(t, __fsub_rn(1.0f, s)), s);
+}
+
 }  // namespace
+
+extern "C" int coset_layer_beta(const float* theta, const float* beta_min, const float* beta_range, int64_t n_tiles,
+                                float* beta, void* stream) {
+    if (n_tiles < 0) return fail(COSET_E_BADARG, "n_tiles is negative");
+    if (n_tiles == 0) return 0;
+    if (!theta || !beta_min || !beta_range || !beta) return fail(COSET_E_BADARG, "null pointer");
+    k_layer_beta<<<(unsigned)((n_tiles + kThreads - 1) / kThreads), kThreads, 0, (cudaStream_t)stream>>>(theta, beta_min, beta_range,
+                                                                                                      n_tiles, beta);
+    return check_launch("layer_beta");
+}
+
+extern "C" int coset_e8_layer_fake_quant_fwd(const float* w, const float* theta, const float* beta_min, const float* beta_range,
+                                             int64_t n_blocks, int64_t blocks_per_tile, int q, float clip, void* out,
+                                             int out_dtype, void* codes, float* beta, void* stream) {
+    if (n_blocks < 0 || blocks_per_tile < 1) return fail(COSET_E_BADARG, "bad n_blocks / blocks_per_tile");
+    const int64_t tiles = (n_blocks + blocks_per_tile - 1) / blocks_per_tile;
+    if (int e = coset_layer_beta(theta, beta_min, beta_range, tiles, beta, stream)) return e;
+    return coset_e8_quantize(w, COSET_DTYPE_F32, beta, COSET_SCALE_MUL_TILE, n_blocks, blocks_per_tile, q, 2, clip, out,
+                             out_dtype, codes, stream);
+}
+
+extern "C" int coset_e8_fake_quant_bwd(const void* grad_out, int grad_dtype, const float* w, const void* codes,
+                                       const float* beta, int64_t n_blocks, int64_t blocks_per_tile, int q, float clip,
+                                       float* grad_w, float* grad_beta, void* stream);
+
+extern "C" int coset_e8_layer_fake_quant_bwd(const void* grad_out, int grad_dtype, const float* w, const void* codes,
+                                             const float* beta, const float* theta, const float* beta_range, int64_t n_blocks,
+                                             int64_t blocks_per_tile, int q, float clip, float* grad_w, float* grad_theta,
+                                             void* stream) {
+    if (int e = coset_e8_fake_quant_bwd(grad_out, grad_dtype, w, codes, beta, n_blocks, blocks_per_tile, q, clip, grad_w,
+                                        grad_theta, stream))
+        return e;
+    if (!grad_theta || n_blocks == 0) return 0;
+    if (!theta || !beta_range) return fail(COSET_E_BADARG, "null pointer");
+    const int64_t tiles = (n_blocks + blocks_per_tile - 1) / blocks_per_tile;
+    k_layer_dtheta<<<(unsigned)((tiles + kThreads - 1) / kThreads), kThreads, 0, (cudaStream_t)stream>>>(theta, beta_range, tiles,
+                                                                                                       grad_theta);
+    return check_launch("layer_dtheta");
+}
 
 extern "C" int coset_e8_fake_quant_bwd(const void* grad_out, int grad_dtype, const float* w, const void* codes,
                                        const float* beta, int64_t n_blocks, int64_t blocks_per_tile, int q,

@@ -21,6 +21,8 @@ using namespace coset;
 namespace {
 
 constexpr int kWarps = 8;
+// residual-table entry of the all-zero level word: every coordinate 2 * 0 + kTableBias
+__device__ __forceinline__ uint2 zero_entry() { return make_uint2(0x07070707u, 0x07070707u); }
 
 template <int XDT>
 __device__ __forceinline__ void load_x8(const void* x, int64_t elem_offset, float (&v)[8]);
@@ -91,7 +93,8 @@ k_vlut_gemv(const uint32_t* __restrict__ codes, const float* __restrict__ beta, 
 #pragma unroll
         for (int j = 0; j < kGroup; ++j) {
             t_lo[j] = __ldg(table + (code_c[j] & 0xffffu));
-            t_hi[j] = __ldg(table + (code_c[j] >> 16));
+            t_hi[j] = zero_entry();  // all-zero top-level word: zero residual, no gather
+            if (code_c[j] >> 16) t_hi[j] = __ldg(table + (code_c[j] >> 16));
         }
 #pragma unroll
         for (int j = 0; j < kGroup; ++j) {
@@ -142,14 +145,266 @@ k_vlut_gemv(const uint32_t* __restrict__ codes, const float* __restrict__ beta, 
     }
 }
 
+// One or two tokens: the product is bound by the latency of ONE dependent chain (code -> table entry ->
+// multiply), so a row is split over kSplit warps of the same CTA and every lane owns at most kOwn blocks
+// whose codes, scales, table entries and activations are ALL requested before the first multiply.  The
+// partial sums of a row are added in a fixed order through shared memory (deterministic, no atomics).
+constexpr int kSplit = 4;              // warps per output row
+constexpr int kRowsPerCta = kWarps / kSplit;
+constexpr int kOwn = 4;                // blocks per lane and pass
+
+template <int TT, int XDT, int MODE, bool CLIP>
+__global__ void __launch_bounds__(kWarps * 32)
+k_vlut_gemv_split(const uint32_t* __restrict__ codes, const float* __restrict__ beta, e8::TileDiv td, int n_out, int kb,
+                  const void* __restrict__ x, int64_t ldx, int T, const float* __restrict__ bias,
+                  const uint2* __restrict__ table, Targets out, int64_t ldy, float clip) {
+    __shared__ float part[kRowsPerCta][kSplit][TT];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r_in = warp / kSplit, part_id = warp % kSplit;
+    const int row = blockIdx.x * kRowsPerCta + r_in;
+    const int t0 = blockIdx.y * TT;
+    float acc[TT];
+#pragma unroll
+    for (int t = 0; t < TT; ++t) acc[t] = 0.0f;
+    if (row < n_out) {
+        const int64_t row_base = (int64_t)row * kb;
+        // lane l of part p owns blocks p*32 + l + j * (32 * kSplit): a warp reads 128 contiguous bytes of codes
+        for (int blk0 = part_id * 32 + lane; blk0 < kb; blk0 += 32 * kSplit * kOwn) {
+            uint32_t code[kOwn];
+            float sc[kOwn];
+#pragma unroll
+            for (int j = 0; j < kOwn; ++j) {
+                const int blk = blk0 + j * 32 * kSplit;
+                code[j] = blk < kb ? __ldcs(codes + row_base + blk) : 0u;
+                sc[j] = (MODE == COSET_SCALE_MUL_TILE && blk < kb) ? __ldg(beta + e8::tile_of(td, row_base + blk)) : 1.0f;
+            }
+            float xv[kOwn][TT][8];
+#pragma unroll
+            for (int j = 0; j < kOwn; ++j) {
+                const int blk = blk0 + j * 32 * kSplit;
+#pragma unroll
+                for (int t = 0; t < TT; ++t) {
+                    if (blk < kb && t0 + t < T) {
+                        load_x8<XDT>(x, (int64_t)(t0 + t) * ldx + (int64_t)blk * 8, xv[j][t]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) xv[j][t][i] = 0.0f;
+                    }
+                }
+            }
+            uint2 t_lo[kOwn], t_hi[kOwn];
+#pragma unroll
+            for (int j = 0; j < kOwn; ++j) {
+                // the residual of an all-zero level word is the zero vector and the top level of a quantiser
+                // that is not overloaded is almost always that word: its gather is skipped
+                t_lo[j] = __ldg(table + (code[j] & 0xffffu));
+                t_hi[j] = zero_entry();
+                if (code[j] >> 16) t_hi[j] = __ldg(table + (code[j] >> 16));
+            }
+#pragma unroll
+            for (int j = 0; j < kOwn; ++j) {
+                float v2[8];
+                e8::twice_from_entries(t_lo[j], t_hi[j], v2);
+                if (CLIP) {
+                    float w[8];
+                    e8::scale_twice<MODE == COSET_SCALE_MUL_TILE ? 2 : 0>(v2, sc[j], w);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v2[i] = fminf(fmaxf(w[i], -clip), clip);
+                }
+                const float half_inv = CLIP ? 1.0f : (MODE == COSET_SCALE_MUL_TILE ? __fdividef(0.5f, sc[j]) : 0.5f);
+#pragma unroll
+                for (int t = 0; t < TT; ++t) {
+                    float d = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) d = __fmaf_rn(v2[i], xv[j][t][i], d);
+                    acc[t] = __fmaf_rn(d, half_inv, acc[t]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < TT; ++t) {
+        float a = acc[t];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane == 0) part[r_in][part_id][t] = a;
+    }
+    __syncthreads();
+    if (part_id == 0 && lane < TT && row < n_out && t0 + lane < T) {
+        float r = part[r_in][0][lane];
+#pragma unroll
+        for (int p = 1; p < kSplit; ++p) r += part[r_in][p][lane];
+        r += bias ? __ldg(bias + row) : 0.0f;
+        for (int k = 0; k < out.n; ++k) out.y[k][(int64_t)(t0 + lane) * ldy + row] = r;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// bf16 activations, up to 16 tokens: the multiply-adds go to the tensor cores (mma.sync m16n8k16, bf16 in,
+// float32 accumulate), which removes them and the per-token handling of the activations from the
+// instruction stream -- the scalar kernel above spends 8 FMA + 8 activation unpacks per block AND token.
+//
+// One CTA owns 16 output rows and the whole K; its warps take interleaved units of 8 blocks (64 values
+// of K) and their partial tiles are added in a fixed order through shared memory (deterministic).
+// Per unit a warp reads the 16 x 8 codes (and scales) as ONE 16-byte vector per lane -- lane l holds row
+// l/2, blocks 4 (l%2) .. 4 (l%2) + 3 -- and hands every code to the four lanes whose A-fragment slots it
+// fills with shuffles: thread (g = lane/4, c = lane%4) of a k16 step needs the weights k = 2c, 2c+1 of two
+// blocks of rows g and g+8, i.e. ONE 32-bit word of each residual-table entry (gathered as such).
+// The bytes become floats through the byte-permute trick, are scaled by 0.5 / beta (clamped when asked)
+// and packed to bf16 pairs.  The activations are the B fragments, read as 32-bit words from x (L1-resident).
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// float(byte `sel` of v) + 1.5 * 2^23, sel = 0..3 at run time
+__device__ __forceinline__ float byte_to_magic_float(uint32_t v, uint32_t sel) {
+    return __uint_as_float(__byte_perm(v, 0x4B400000u, 0x7640u + sel));
+}
+
+constexpr int kMmaWarps = 8;  // K is split over the warps of a CTA (16 warps measured slower: one CTA per SM, two waves)
+
+template <int MODE, bool CLIP, int NT>
+__global__ void __launch_bounds__(kMmaWarps * 32)
+k_vlut_mma(const uint32_t* __restrict__ codes, const float* __restrict__ beta, int64_t blocks_per_tile, int n_out, int kb,
+           const __nv_bfloat16* __restrict__ x, int64_t ldx, int T, const float* __restrict__ bias,
+           const uint2* __restrict__ table, Targets out, int64_t ldy, float clip) {
+    __shared__ float part[kMmaWarps][16][8 * NT + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, c = lane & 3;
+    const int row0 = blockIdx.x * 16;
+    const int t0 = blockIdx.y * (8 * NT);
+    const int units = kb >> 3;
+    // loading role: row l/2, blocks 4 (l%2) .. +3 of the unit
+    const int lrow = row0 + (lane >> 1);
+    const bool lrow_ok = lrow < n_out;
+    const int64_t lbase = (int64_t)lrow * kb + (lane & 1) * 4;
+    const bool per_block = MODE == COSET_SCALE_MUL_TILE && blocks_per_tile == 1;
+    float d[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) d[n][0] = d[n][1] = d[n][2] = d[n][3] = 0.0f;
+    const uint32_t wsel = (uint32_t)(c >> 1);          // which 32-bit word of a table entry holds k = 2c, 2c+1
+    const uint32_t bsel = (uint32_t)((c & 1) * 2);     // first of the two bytes inside that word
+    const char* table_w = reinterpret_cast<const char*>(table) + wsel * 4;
+    const float kOff = 12582912.0f + 5.0f * e8::kTableBias;
+    // activations of this thread's B fragments: token t0 + 8 n + g, k = k0 + 2c (+8)
+    const __nv_bfloat16* xrow[NT];
+    bool xok[NT];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        const int t = t0 + 8 * n + g;
+        xok[n] = t < T;
+        xrow[n] = x + (int64_t)(xok[n] ? t : 0) * ldx + 2 * c;
+    }
+    auto load_unit = [&](int u, uint4& cv, float4& iv) {
+        cv = make_uint4(0u, 0u, 0u, 0u);
+        iv = make_float4(0.5f, 0.5f, 0.5f, 0.5f);
+        if (lrow_ok && u < units) {
+            cv = __ldcs(reinterpret_cast<const uint4*>(codes + lbase + (int64_t)u * 8));
+            if (per_block) {
+                const float4 b = __ldcs(reinterpret_cast<const float4*>(beta + lbase + (int64_t)u * 8));
+                iv = make_float4(__fdividef(0.5f, b.x), __fdividef(0.5f, b.y), __fdividef(0.5f, b.z), __fdividef(0.5f, b.w));
+            } else if (MODE == COSET_SCALE_MUL_TILE) {
+                const float b = __ldg(beta + (lbase + (int64_t)u * 8) / blocks_per_tile);
+                const float r = __fdividef(0.5f, b);
+                iv = make_float4(r, r, r, r);
+            }
+        }
+    };
+    uint4 cv_n;
+    float4 iv_n;
+    load_unit(warp, cv_n, iv_n);
+    for (int u = warp; u < units; u += kMmaWarps) {
+        const uint4 cv = cv_n;
+        const float4 iv = iv_n;
+        load_unit(u + kMmaWarps, cv_n, iv_n);
+        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+        const float iw[4] = {iv.x, iv.y, iv.z, iv.w};
+        // codes and inverse scales of this thread's slots: step s uses blocks 2s, 2s+1 of rows g, g+8
+        uint32_t code[4][4];
+        float inv[4][4];
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {  // j: 0 = (g, 2s), 1 = (g+8, 2s), 2 = (g, 2s+1), 3 = (g+8, 2s+1)
+                const int blk = 2 * s + (j >> 1);
+                const int src = 2 * (g + 8 * (j & 1)) + (blk >> 2);
+                code[s][j] = __shfl_sync(0xffffffffu, cw[blk & 3], src);
+                inv[s][j] = __shfl_sync(0xffffffffu, iw[blk & 3], src);
+            }
+        }
+        uint32_t wlo[4][4], whi[4][4];
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                wlo[s][j] = __ldg(reinterpret_cast<const uint32_t*>(table_w + (size_t)(code[s][j] & 0xffffu) * 8));
+                whi[s][j] = 0x07070707u;  // all-zero top-level word: zero residual, no gather
+                if (code[s][j] >> 16) whi[s][j] = __ldg(reinterpret_cast<const uint32_t*>(table_w + (size_t)(code[s][j] >> 16) * 8));
+            }
+        }
+        const int k0 = u * 64;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            uint32_t a[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t bytes = wlo[s][j] + 4u * whi[s][j];
+                float w0 = __fmul_rn(__fsub_rn(byte_to_magic_float(bytes, bsel), kOff), inv[s][j]);
+                float w1 = __fmul_rn(__fsub_rn(byte_to_magic_float(bytes, bsel + 1u), kOff), inv[s][j]);
+                if (CLIP) {
+                    w0 = fminf(fmaxf(w0, -clip), clip);
+                    w1 = fminf(fmaxf(w1, -clip), clip);
+                }
+                __nv_bfloat162 h = __floats2bfloat162_rn(w0, w1);
+                a[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                uint32_t b0 = 0u, b1 = 0u;
+                if (xok[n]) {
+                    b0 = __ldg(reinterpret_cast<const uint32_t*>(xrow[n] + k0 + 16 * s));
+                    b1 = __ldg(reinterpret_cast<const uint32_t*>(xrow[n] + k0 + 16 * s + 8));
+                }
+                mma_bf16_16816(d[n], a, b0, b1);
+            }
+        }
+    }
+
+    // accumulator layout: d[0], d[1] = (row g, tokens 2c, 2c+1); d[2], d[3] = (row g+8, same tokens)
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        part[warp][g][8 * n + 2 * c] = d[n][0];
+        part[warp][g][8 * n + 2 * c + 1] = d[n][1];
+        part[warp][g + 8][8 * n + 2 * c] = d[n][2];
+        part[warp][g + 8][8 * n + 2 * c + 1] = d[n][3];
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 16 * 8 * NT; e += kMmaWarps * 32) {
+        const int r = e & 15, t = e >> 4;  // consecutive threads write consecutive rows of one token
+        if (row0 + r < n_out && t0 + t < T) {
+            float v = part[0][r][t];
+#pragma unroll
+            for (int w = 1; w < kMmaWarps; ++w) v += part[w][r][t];
+            v += bias ? __ldg(bias + row0 + r) : 0.0f;
+            for (int k = 0; k < out.n; ++k) out.y[k][(int64_t)(t0 + t) * ldy + row0 + r] = v;
+        }
+    }
+}
+
 template <int XDT, int MODE, bool CLIP>
 void launch_gemv(int tt, dim3 grid, cudaStream_t st, const uint32_t* codes, const float* beta, e8::TileDiv td, int n_out,
                  int kb, const void* x, int64_t ldx, int T, const float* bias, const uint2* table, const Targets& y, int64_t ldy,
                  float clip) {
 #define GEMV_CASE(TT) k_vlut_gemv<TT, XDT, MODE, CLIP><<<grid, kWarps * 32, 0, st>>>(codes, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy, clip)
+    if (tt <= 2) {  // one or two tokens: the split-row kernel
+        dim3 sgrid((n_out + kRowsPerCta - 1) / kRowsPerCta, grid.y);
+        if (tt == 1) k_vlut_gemv_split<1, XDT, MODE, CLIP><<<sgrid, kWarps * 32, 0, st>>>(codes, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy, clip);
+        else k_vlut_gemv_split<2, XDT, MODE, CLIP><<<sgrid, kWarps * 32, 0, st>>>(codes, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy, clip);
+        return;
+    }
     switch (tt) {
-        case 1: GEMV_CASE(1); break;
-        case 2: GEMV_CASE(2); break;
         case 4: GEMV_CASE(4); break;
         case 8: GEMV_CASE(8); break;
         default: GEMV_CASE(16); break;
@@ -181,6 +436,25 @@ static int vlut_gemv_impl(const void* codes, const float* beta, int64_t blocks_p
     if (grid.y > 65535) return fail(COSET_E_UNSUPPORTED, "T too large for the small-T kernel");
     const uint32_t* c = (const uint32_t*)codes;
     if (!(clip == clip)) return fail(COSET_E_BADARG, "clip is not a number");
+    // bf16 activations, three tokens or more: tensor-core kernel when the layout allows 16-byte code vectors and
+    // whole units per scale tile (one or two tokens are faster in the split-row kernel: 11 us against 17 us)
+    if (T >= 3 && x_dtype == COSET_DTYPE_BF16 && (kb % 8) == 0 && aligned(codes, 16) && (ldx % 2) == 0 &&
+        (!beta || blocks_per_tile == 1 || (blocks_per_tile % 8) == 0) && (!beta || blocks_per_tile != 1 || aligned(beta, 16))) {
+        const int nt = T > 8 ? 2 : 1;
+        dim3 mgrid((n_out + 15) / 16, (T + 8 * nt - 1) / (8 * nt));
+        if (mgrid.y > 65535) return fail(COSET_E_UNSUPPORTED, "T too large for the small-T kernel");
+        const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+#define MMA_LAUNCH(MODE, CLIPB, NT) k_vlut_mma<MODE, CLIPB, NT><<<mgrid, kMmaWarps * 32, 0, st>>>(c, beta, beta ? blocks_per_tile : 1, n_out, kb, xb, ldx, T, bias, table, y, ldy, clip)
+        if (beta) {
+            if (clip > 0.0f) { if (nt == 2) MMA_LAUNCH(2, true, 2); else MMA_LAUNCH(2, true, 1); }
+            else { if (nt == 2) MMA_LAUNCH(2, false, 2); else MMA_LAUNCH(2, false, 1); }
+        } else {
+            if (clip > 0.0f) { if (nt == 2) MMA_LAUNCH(0, true, 2); else MMA_LAUNCH(0, true, 1); }
+            else { if (nt == 2) MMA_LAUNCH(0, false, 2); else MMA_LAUNCH(0, false, 1); }
+        }
+#undef MMA_LAUNCH
+        return check_launch("e8_vlut_gemv (tensor-core form)");
+    }
 #define GEMV_LAUNCH(XDT, MODE)                                                                                              \
     if (clip > 0.0f) launch_gemv<XDT, MODE, true>(tt, grid, st, c, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy, clip); \
     else launch_gemv<XDT, MODE, false>(tt, grid, st, c, beta, td, n_out, kb, x, ldx, T, bias, table, y, ldy, 0.0f)

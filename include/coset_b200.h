@@ -141,6 +141,26 @@ int coset_e8_fake_quant_bwd(const void* grad_out, int grad_dtype, const float* w
                             float clip, float* grad_w, float* grad_beta, void* stream);
 
 /*
+ * The layer's weight path with its scale computed on the device (coset/core/layers.py:415-470):
+ *   beta[t] = beta_min[t] + sigmoid(theta[t]) * beta_range[t]        (one value per tile)
+ *   out     = clamp(e8_quantize(W * beta) / beta, +-clip)            (coset_e8_quantize, M = 2)
+ * coset_layer_beta is the first line alone; coset_e8_layer_fake_quant_fwd is both (two launches, one
+ * call) and leaves the scales it used in `beta` and the packed codes in `codes` for the backward pass;
+ * coset_e8_layer_fake_quant_bwd is coset_e8_fake_quant_bwd followed by the chain rule through the
+ * sigmoid: grad_theta = (dbeta * beta_range) * (1 - s) * s, as torch autograd forms it (grad_theta may be
+ * NULL when theta is not trained).
+ */
+int coset_layer_beta(const float* theta, const float* beta_min, const float* beta_range, int64_t n_tiles,
+                     float* beta, void* stream);
+int coset_e8_layer_fake_quant_fwd(const float* w, const float* theta, const float* beta_min, const float* beta_range,
+                                  int64_t n_blocks, int64_t blocks_per_tile, int q, float clip, void* out,
+                                  int out_dtype, void* codes, float* beta, void* stream);
+int coset_e8_layer_fake_quant_bwd(const void* grad_out, int grad_dtype, const float* w, const void* codes,
+                                  const float* beta, const float* theta, const float* beta_range, int64_t n_blocks,
+                                  int64_t blocks_per_tile, int q, float clip, float* grad_w, float* grad_theta,
+                                  void* stream);
+
+/*
  * Host-buffer variants: the arrays live in HOST memory (page-locked for full overlap); the
  * library stages them through a context's device slots, chunk by chunk, with copies in both
  * directions overlapping the kernels.  This is the call a CPU-side caller of the reference's
