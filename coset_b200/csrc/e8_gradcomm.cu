@@ -28,46 +28,25 @@ struct PeerStreams {
     int first;
 };
 
-template <int DT, bool PEERS>
-__global__ void __launch_bounds__(kThreads)
-k_decode_mean(const uint32_t* __restrict__ codes, PeerStreams peers, int world, int64_t n, int64_t stride, float divisor,
-              const uint2* __restrict__ table, void* __restrict__ out, const int* __restrict__ status) {
-    int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    if (b >= n) return;
-    // a bounded cross-rank wait before this launch gave up: the peers' streams are not known to be
-    // complete, so nothing is read or written
-    if (PEERS && status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
+// One thread owns kPerThread consecutive blocks: it requests a 16-byte vector of codes from every stream
+// before the first table lookup (W x 16 bytes in flight per thread, which is what keeps NVLink busy when the
+// streams are the peers' buffers), accumulates the W reconstructions per block and writes 128 contiguous bytes.
+constexpr int kPerThread = 1;
+
+__device__ __forceinline__ void accumulate_code(uint32_t code, const uint2* __restrict__ table, uint32_t (&acc)[4]) {
+    const uint2 t0 = __ldg(table + (code & 0xffffu));
+    uint2 t1 = make_uint2(0x07070707u, 0x07070707u);  // all-zero top-level word: zero residual, no lookup
+    if (code >> 16) t1 = __ldg(table + (code >> 16));
+    const uint32_t lo = t0.x + 4u * t1.x, hi = t0.y + 4u * t1.y;  // biased bytes, each <= 90
+    acc[0] += lo & 0x00ff00ffu;
+    acc[1] += (lo >> 8) & 0x00ff00ffu;
+    acc[2] += hi & 0x00ff00ffu;
+    acc[3] += (hi >> 8) & 0x00ff00ffu;
+}
+
+template <int DT>
+__device__ __forceinline__ void store_mean(const uint32_t (&acc)[4], int world, float divisor, void* __restrict__ out, int64_t b) {
     // 16-bit lanes: acc[0] = coordinates (0,2), acc[1] = (1,3), acc[2] = (4,6), acc[3] = (5,7)
-    uint32_t acc[4] = {0u, 0u, 0u, 0u};
-    for (int r0 = 0; r0 < world; r0 += 4) {
-      uint32_t c4[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {  // up to four streams requested before the first table lookup
-        const int r = r0 + u;
-        c4[u] = 0u;
-        if (r < world) {
-            if (PEERS) {
-                int src = peers.first + r;
-                if (src >= world) src -= world;
-                c4[u] = __ldcs(peers.p[src] + b);
-            } else {
-                c4[u] = __ldcs(codes + (int64_t)r * stride + b);
-            }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (r0 + u >= world) break;
-        const uint32_t code = c4[u];
-        uint2 t0 = __ldg(table + (code & 0xffffu));
-        uint2 t1 = __ldg(table + (code >> 16));
-        uint32_t lo = t0.x + 4u * t1.x, hi = t0.y + 4u * t1.y;  // biased bytes, each <= 90
-        acc[0] += lo & 0x00ff00ffu;
-        acc[1] += (lo >> 8) & 0x00ff00ffu;
-        acc[2] += hi & 0x00ff00ffu;
-        acc[3] += (hi >> 8) & 0x00ff00ffu;
-      }
-    }
     const int bias = 5 * e8::kTableBias * world;  // every rank contributes 7 + 4*7 to each lane
     int v[8];
     v[0] = (int)(acc[0] & 0xffffu) - bias; v[2] = (int)(acc[0] >> 16) - bias;
@@ -77,11 +56,68 @@ k_decode_mean(const uint32_t* __restrict__ codes, PeerStreams peers, int world, 
     float o[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        float sum = __fmul_rn((float)v[i], 0.5f);  // exact: |v| < 2^16
+        const float sum = __fmul_rn((float)v[i], 0.5f);  // exact: |v| < 2^16
         o[i] = __fdiv_rn(sum, divisor);
     }
     e8::Row8<DT>::store(out, b, o);
 }
+
+template <int DT, bool PEERS>
+__global__ void __launch_bounds__(kThreads)
+k_decode_mean(const uint32_t* __restrict__ codes, PeerStreams peers, int world, int64_t n, int64_t stride, float divisor,
+              const uint2* __restrict__ table, void* __restrict__ out, const int* __restrict__ status) {
+    const int64_t b0 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) * kPerThread;
+    if (b0 >= n) return;
+    // a bounded cross-rank wait before this launch gave up: the peers' streams are not known to be
+    // complete, so nothing is read or written
+    if (PEERS && status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
+    uint32_t acc[kPerThread][4];
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0u;
+    auto stream_ptr = [&](int r) -> const uint32_t* {
+        if (PEERS) {
+            int src = peers.first + r;
+            if (src >= world) src -= world;
+            return peers.p[src] + b0;
+        }
+        return codes + (int64_t)r * stride + b0;
+    };
+    // vector path when a stream's 16 bytes at b0 are aligned and inside the tensor; else (odd strides, the
+    // tail of the tensor) four scalar loads
+    const bool full = b0 + kPerThread <= n;
+    for (int r0 = 0; r0 < world; r0 += 4) {
+        uint32_t c4[4][kPerThread];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {  // up to four streams requested before the first table lookup
+#pragma unroll
+            for (int j = 0; j < kPerThread; ++j) c4[u][j] = 0u;
+            if (r0 + u < world) {
+                const uint32_t* p = stream_ptr(r0 + u);
+                if (full && ((reinterpret_cast<uintptr_t>(p) & 15u) == 0)) {
+                    const uint4 v = __ldcs(reinterpret_cast<const uint4*>(p));
+                    c4[u][0] = v.x; c4[u][1] = v.y; c4[u][2] = v.z; c4[u][3] = v.w;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < kPerThread; ++j)
+                        if (b0 + j < n) c4[u][j] = __ldcs(p + j);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (r0 + u >= world) break;
+#pragma unroll
+            for (int j = 0; j < kPerThread; ++j) accumulate_code(c4[u][j], table, acc[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j)
+        if (b0 + j < n) store_mean<DT>(acc[j], world, divisor, out, b0 + j);
+}
+
+}  // namespace
+
+namespace {
 
 // Cross-rank "everyone has arrived" with a bound.  flags[r] is rank r's own array of `world` words
 // (peer / symmetric memory, mapped into this process); word s of it is written only by rank s.
@@ -148,7 +184,7 @@ extern "C" int coset_e8_decode_mean(const void* codes, int world, int64_t n_bloc
     const uint2* table = residual_table_q4(st);
     if (!table) return COSET_E_STATE;
     float divisor = scale * (float)world;  // one float32 rounding, reproduced by the CPU recipe
-    unsigned grid = (unsigned)((n_blocks + kThreads - 1) / kThreads);
+    unsigned grid = (unsigned)((n_blocks + (int64_t)kThreads * kPerThread - 1) / ((int64_t)kThreads * kPerThread));
     PeerStreams none = {};
     if (out_dtype == COSET_DTYPE_F32)
         k_decode_mean<0, false><<<grid, kThreads, 0, st>>>((const uint32_t*)codes, none, world, n_blocks, rank_stride_blocks, divisor, table, out, nullptr);
@@ -177,7 +213,7 @@ extern "C" int coset_e8_decode_mean_peers(const void* const* rank_codes, int wor
     const uint2* table = residual_table_q4(st);
     if (!table) return COSET_E_STATE;
     float divisor = scale * (float)world;
-    unsigned grid = (unsigned)((n_blocks + kThreads - 1) / kThreads);
+    unsigned grid = (unsigned)((n_blocks + (int64_t)kThreads * kPerThread - 1) / ((int64_t)kThreads * kPerThread));
     if (out_dtype == COSET_DTYPE_F32)
         k_decode_mean<0, true><<<grid, kThreads, 0, st>>>(nullptr, peers, world, n_blocks, 0, divisor, table, out, status);
     else
