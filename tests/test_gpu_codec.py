@@ -312,3 +312,27 @@ def test_bulk_config_properties(e8):
     codes2 = e8.e8_encode_packed(xh, scale=beta, scale_mode=MT)
     same = (codes2.view(torch.int32) == codes.view(torch.int32)).float().mean()
     assert same > 0.99  # re-encoding a reconstruction returns the same code (CPU restatement: 99.87 %)
+
+
+def test_encode_on_concurrent_streams_and_growing_sizes(e8):
+    """The codes-only encoder keeps library-owned scratch per (device, stream): calls issued on several
+    streams at once must not disturb each other, a larger tensor on the same stream grows the scratch,
+    and an overloaded tensor (most blocks deferred: the fix-up kernel's sweep) leaves the scratch clean
+    for the next call."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    sizes = [4096, 300_000, 70_001, 1_200_000]
+    xs = [torch.randn(n, 8, device="cuda", generator=g) * (0.5 if i != 2 else 6.0) for i, n in enumerate(sizes)]
+    xs[1][::97, 3] = 5.0  # exact integers: deferred blocks in an otherwise easy tensor
+    want = [e8.e8_encode_packed(x, literal=True).view(torch.int32).clone() for x in xs]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream() for _ in range(3)]
+    got = {}
+    for rep in range(3):
+        for i, x in enumerate(xs):
+            st = streams[(i + rep) % 3]
+            st.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st):
+                got[(rep, i)] = e8.e8_encode_packed(x).view(torch.int32)
+    torch.cuda.synchronize()
+    for (rep, i), c in got.items():
+        assert torch.equal(c, want[i]), (rep, i, int((c != want[i]).sum()))
