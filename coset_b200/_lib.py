@@ -38,7 +38,7 @@ SIGNATURES = {
     "coset_e8_decode_mean": [_vp, _i32, _i64, _i64, _f32, _vp, _i32, _vp],
     "coset_e8_decode_mean_peers": [_vp, _i32, _i32, _i64, _f32, _vp, _i32, _vp, _vp],
     "coset_peer_signal_wait": [_vp, _i32, _i32, ctypes.c_uint32, _i32, _vp, _vp],
-    "coset_e8_vlut_gemv": [_vp, _vp, _i64, _i32, _i32, _vp, _i32, _i64, _i32, _vp, _vp, _i64, _f32, _vp],
+    "coset_e8_vlut_gemv": [_vp, _vp, _i64, _i32, _i32, _vp, _i32, _i64, _i32, _vp, _vp, _i32, _i64, _f32, _vp],
     "coset_e8_vlut_gemv_scatter": [_vp, _vp, _i64, _i32, _i32, _vp, _i32, _i64, _i32, _vp, _vp, _i32, _i64, _f32, _vp],
     "coset_e8_quant_stats_scratch_bytes": [_i64],
     "coset_e8_quant_stats": [_vp, _i32, _vp, _i32, _i64, _i64, _vp, _i64, _vp, _vp],

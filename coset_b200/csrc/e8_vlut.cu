@@ -50,7 +50,14 @@ constexpr int kMaxTargets = 16;
 struct Targets {
     float* y[kMaxTargets];
     int n;
+    int bf16;  // 1: the buffers hold bf16 values (results are rounded to nearest even on the store)
 };
+__device__ __forceinline__ void store_result(const Targets& out, int64_t idx, float r) {
+    for (int k = 0; k < out.n; ++k) {
+        if (out.bf16) reinterpret_cast<__nv_bfloat16*>(out.y[k])[idx] = __float2bfloat16_rn(r);
+        else out.y[k][idx] = r;
+    }
+}
 
 // CLIP: the weights are clamp(decode / beta, +-clip) as the training layer applies it
 // (coset/core/layers.py:463); the clamp acts on single weights, so every weight is scaled first.
@@ -140,7 +147,7 @@ k_vlut_gemv(const uint32_t* __restrict__ codes, const float* __restrict__ beta, 
         for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
         if (lane == 0 && t0 + t < T) {
             const float r = a + (bias ? __ldg(bias + row) : 0.0f);
-            for (int k = 0; k < out.n; ++k) out.y[k][(int64_t)(t0 + t) * ldy + row] = r;
+            store_result(out, (int64_t)(t0 + t) * ldy + row, r);
         }
     }
 }
@@ -235,7 +242,7 @@ k_vlut_gemv_split(const uint32_t* __restrict__ codes, const float* __restrict__ 
 #pragma unroll
         for (int p = 1; p < kSplit; ++p) r += part[r_in][p][lane];
         r += bias ? __ldg(bias + row) : 0.0f;
-        for (int k = 0; k < out.n; ++k) out.y[k][(int64_t)(t0 + lane) * ldy + row] = r;
+        store_result(out, (int64_t)(t0 + lane) * ldy + row, r);
     }
 }
 
@@ -388,7 +395,7 @@ k_vlut_mma(const uint32_t* __restrict__ codes, const float* __restrict__ beta, i
 #pragma unroll
             for (int w = 1; w < kMmaWarps; ++w) v += part[w][r][t];
             v += bias ? __ldg(bias + row0 + r) : 0.0f;
-            for (int k = 0; k < out.n; ++k) out.y[k][(int64_t)(t0 + t) * ldy + row0 + r] = v;
+            store_result(out, (int64_t)(t0 + t) * ldy + row0 + r, v);
         }
     }
 }
@@ -468,12 +475,14 @@ static int vlut_gemv_impl(const void* codes, const float* beta, int64_t blocks_p
 }
 
 extern "C" int coset_e8_vlut_gemv(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
-                                  const void* x, int x_dtype, int64_t ldx, int T, const float* bias, float* y,
-                                  int64_t ldy, float clip, void* stream) {
+                                  const void* x, int x_dtype, int64_t ldx, int T, const float* bias, void* y,
+                                  int y_dtype, int64_t ldy, float clip, void* stream) {
     if (!y && n_out > 0 && T > 0) return fail(COSET_E_BADARG, "null pointer");
+    if (y_dtype != COSET_DTYPE_F32 && y_dtype != COSET_DTYPE_BF16) return fail(COSET_E_BADARG, "unknown y_dtype");
     Targets t = {};
-    t.y[0] = y;
+    t.y[0] = (float*)y;
     t.n = 1;
+    t.bf16 = y_dtype == COSET_DTYPE_BF16 ? 1 : 0;
     return vlut_gemv_impl(codes, beta, blocks_per_tile, n_out, n_in, x, x_dtype, ldx, T, bias, t, ldy, clip, stream);
 }
 

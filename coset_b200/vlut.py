@@ -21,9 +21,9 @@ from .core.e8.codecs import e8_decode_packed, e8_encode_packed
 
 
 def e8_vlut_matmul(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_per_tile: int, x: torch.Tensor,
-                   bias: Optional[torch.Tensor] = None, clip: float = 0.0) -> torch.Tensor:
+                   bias: Optional[torch.Tensor] = None, clip: float = 0.0, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
     """y = x @ Wq.T + bias with Wq = decode(codes) / beta (clamped to +-clip when clip > 0);
-    codes int32 [n_out, n_in / 8]; x [T, n_in]."""
+    codes int32 [n_out, n_in / 8]; x [T, n_in]; y float32, or bf16 rounded once from the float32 sums."""
     _lib.require_cuda(codes, "codes")
     _lib.require_cuda(x, "x")
     if codes.dtype != torch.int32 or codes.dim() != 2 or not codes.is_contiguous():
@@ -33,14 +33,14 @@ def e8_vlut_matmul(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_per
         raise ValueError(f"x must be [T, {kb * 8}], got {tuple(x.shape)}")
     x = x.contiguous()
     T = x.shape[0]
-    y = torch.empty((T, n_out), dtype=torch.float32, device=x.device)
+    y = torch.empty((T, n_out), dtype=out_dtype, device=x.device)
     b = beta.to(torch.float32).contiguous().view(-1) if beta is not None else None
     bias32 = bias.to(torch.float32).contiguous() if bias is not None else None
     with torch.cuda.device(x.device):
         rc = _lib.lib().coset_e8_vlut_gemv(_lib.ptr(codes), _lib.ptr(b) if b is not None else None, int(blocks_per_tile),
                                            n_out, kb * 8, _lib.ptr(x), _lib.dtype_code(x, "x"), x.stride(0), T,
-                                           _lib.ptr(bias32) if bias32 is not None else None, _lib.ptr(y), y.stride(0),
-                                           float(clip), _lib.stream())
+                                           _lib.ptr(bias32) if bias32 is not None else None, _lib.ptr(y),
+                                           _lib.dtype_code(y, "y"), y.stride(0), float(clip), _lib.stream())
     _lib.check(rc, "coset_e8_vlut_gemv")
     return y
 
@@ -164,8 +164,9 @@ class E8CodeLinear(nn.Module):
         x2 = x.reshape(-1, self.in_features)
         clip = self.weight_clip_value
         if x2.shape[0] <= self.small_t_max:
-            y = e8_vlut_matmul(self.codes, self.beta, self.blocks_per_tile, x2, self.bias, clip)
-            y = y.to(x.dtype) if x.dtype != torch.float32 else y
+            out_dtype = torch.bfloat16 if x.dtype == torch.bfloat16 else torch.float32
+            y = e8_vlut_matmul(self.codes, self.beta, self.blocks_per_tile, x2, self.bias, clip, out_dtype)
+            y = y.to(x.dtype) if x.dtype != out_dtype else y
         else:
             if x2.dtype == torch.float32:
                 y = torch.nn.functional.linear(x2, self.dense_weight(torch.float32), self.bias)

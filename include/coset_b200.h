@@ -233,14 +233,15 @@ int coset_peer_signal_wait(void* const* rank_flags, int world, int rank, uint32_
  *   codes : [n_out, n_in/8] packed q=4, M=2 codes (row-major, as coset_e8_quantize emits them)
  *   beta  : per-tile scale in the layer convention (may be NULL = no scale);
  *           blocks_per_tile = n_in/8 for one scale per row, 1 for one per block
- *   x     : [T, ldx] float32 or bf16 (rows 16-byte aligned);  y: [T, ldy] float32
+ *   x     : [T, ldx] float32 or bf16 (rows 16-byte aligned);  y: [T, ldy] float32 or bf16 (y_dtype; accumulated in
+ *           float32 and rounded once on the store)
  *   clip  : > 0: every weight is clamp(decode / beta, +-clip), the layer's weight_clip_value
  *           (coset/core/layers.py:463), so that an exported layer computes what the trained one did; 0: none
  * Memory-bound on the code stream; meant for T <= ~64 (larger T: dequantise + tensor cores).
  */
 int coset_e8_vlut_gemv(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
-                       const void* x, int x_dtype, int64_t ldx, int T, const float* bias, float* y,
-                       int64_t ldy, float clip, void* stream);
+                       const void* x, int x_dtype, int64_t ldx, int T, const float* bias, void* y,
+                       int y_dtype, int64_t ldy, float clip, void* stream);
 /*
  * The same product with the result rows written into SEVERAL buffers at once: y_targets (host array of
  * n_targets <= 16 device pointers) are the places of this rank's output-feature slice in the result
