@@ -114,6 +114,9 @@ def iter_qat(cases=None):
 
         ms = cuda_time(step)
         ms_graph = graph_step_time(layer, x, t)
+        from .core.layers import GraphedTrainStep
+        gstep = GraphedTrainStep(layer, lambda y, tt: ((y - tt).float() ** 2).mean(), (x, t))
+        ms_gstep = cuda_time(lambda: gstep(x, t))
         beta = layer._beta().detach()
         bpt = layer.blocks_per_row if tiling == "row" else 1
         w = layer.weight.detach()
@@ -124,6 +127,7 @@ def iter_qat(cases=None):
             "bench": "qat_step", "weights": tag, "tiling": tiling, "tokens": tokens, "shape": [d_out, d_in],
             "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3),
             "graph_ms_per_step": ms_graph, "graph_tokens_per_s": tokens / (ms_graph * 1e-3),
+            "graphed_train_step_ms": ms_gstep, "graphed_train_step_tokens_per_s": tokens / (ms_gstep * 1e-3),
             "note": "eager steps are bound by the Python / launch path; the graph replays the same forward + backward",
             "gemm_tflops_equiv": 3 * 2 * tokens * d_in * d_out / (ms * 1e-3) / 1e12,
             "fake_quant_fwd_ms": fq, "fake_quant_fwd_GBps": fq_bytes / (fq * 1e-3) / 1e9,

@@ -195,3 +195,37 @@ def test_training_step_is_graph_capturable():
     torch.cuda.synchronize()
     assert torch.equal(gw, layer.weight.grad)
     assert torch.allclose(gt, layer.theta_beta.grad, rtol=1e-6, atol=0)
+
+
+def test_graphed_train_step_keeps_the_statistics_schedule():
+    """GraphedTrainStep replays forward + loss + backward as one CUDA graph and does the layer's host-side
+    bookkeeping itself: after 520 steps (two statistics updates, weights changed in between) the EMA
+    buffers, the step counter, the loss and the gradients are those of 520 eager steps."""
+    from coset_b200.core.e8 import create_e8_hnlq_linear
+    from coset_b200.core.layers import GraphedTrainStep
+    torch.manual_seed(0)
+    a = create_e8_hnlq_linear(64, 48, q=4, M=2, init_kwargs={"std": 20.0}, device="cuda")
+    b = create_e8_hnlq_linear(64, 48, q=4, M=2, device="cuda")
+    b.load_state_dict(a.state_dict())
+    x = torch.randn(32, 64, device="cuda")
+    t = torch.randn(32, 48, device="cuda")
+    loss_fn = lambda y, tt: ((y - tt) ** 2).mean()
+    step = GraphedTrainStep(b, loss_fn, (x, t))
+    assert int(b.step_count) == int(a.step_count) == 0
+    delta = torch.randn_like(a.weight) * 3.0
+    for i in range(1, 521):
+        a.zero_grad(set_to_none=True)
+        la = loss_fn(a(x), t)
+        la.backward()
+        lb = step(x, t)
+        if i == 300:
+            with torch.no_grad():
+                a.weight.add_(delta)
+                b.weight.add_(delta)
+    torch.cuda.synchronize()
+    assert int(a.step_count) == int(b.step_count) == 520
+    assert torch.equal(a.sigma_ema, b.sigma_ema) and torch.equal(a.xmax_ema, b.xmax_ema)
+    assert not torch.equal(a.sigma_ema, torch.ones_like(a.sigma_ema))
+    assert torch.equal(la, lb)
+    assert torch.equal(a.weight.grad, b.weight.grad)
+    assert torch.allclose(a.theta_beta.grad, b.theta_beta.grad, rtol=1e-6, atol=0)
