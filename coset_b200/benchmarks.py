@@ -5,7 +5,7 @@ exist, pyproject.toml:67).  One JSON line per measurement:
     python -m coset_b200.benchmarks vlut       # code-domain matmul, W [4096, 4096], T in {1, 16, 256, 4096}
     python -m torch.distributed.run --nproc-per-node N -m coset_b200.benchmarks gradcomm
                                                # E8-quantised gradient exchange, BERT-base-shaped gradient
-    python -m coset_b200.benchmarks profile-gemv | profile-gemm
+    python -m coset_b200.benchmarks profile-gemv | profile-gemv16 | profile-gemm
                                                # small fixed cases of the two matmul kernels for a profiler capture
 
 Timing: CUDA events on the current stream, warm-up first, inputs resident on the device.
@@ -323,7 +323,7 @@ def bench_gradcomm():
 
 def profile_case(which):
     """Small fixed cases for a profiler capture (W 4096 x 4096, per-block scales, bf16 tokens):
-    `profile-gemv` runs the few-token code-domain product five times at T = 1, `profile-gemm` the
+    `profile-gemv` / `profile-gemv16` run the few-token code-domain product five times at T = 1 / 16, `profile-gemm` the
     fused tcgen05 dequant-GEMM three times at T = 2048 and checks its status word."""
     from .vlut import E8CodeLinear, e8_dequant_gemm
     torch.manual_seed(0)
@@ -331,8 +331,8 @@ def profile_case(which):
     W = (torch.randn(n, n) * 0.02).cuda()
     beta = torch.full((n * n // 8,), 25.0, device="cuda")
     lin = E8CodeLinear.from_weight(W, beta, 1)
-    if which == "profile-gemv":
-        x = torch.randn(1, n, device="cuda").to(torch.bfloat16)
+    if which in ("profile-gemv", "profile-gemv16"):
+        x = torch.randn(1 if which == "profile-gemv" else 16, n, device="cuda").to(torch.bfloat16)
         for _ in range(5):
             lin(x)
     else:
@@ -346,7 +346,7 @@ def profile_case(which):
 def main(argv=None):
     argv = sys.argv[1:] if argv is None else argv
     which = argv[0] if argv else "all"
-    if which in ("profile-gemv", "profile-gemm"):
+    if which in ("profile-gemv", "profile-gemv16", "profile-gemm"):
         profile_case(which)
         return
     if which in ("qat", "all"):
