@@ -231,15 +231,27 @@ torch.cuda.set_device(local)
 dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 via_nccl = E8GradientExchange(scale=500.0)
 via_peer = E8GradientExchange(scale=500.0, transport="peer")
+chunked = E8GradientExchange(scale=500.0, transport="peer", chunks=4)
+chunked.CHUNK_MIN_BLOCKS = 4096  # cut these small gradients into pieces too: decode of piece k beside the encode of piece k+1
 n_values = 8 * 50000 + 3
 for it in range(6):  # several calls in a row: both halves of the double buffer are reused; two sizes alternate
     g = torch.Generator().manual_seed(1000 * it + rank)
-    grad = (torch.randn(n_values if it % 2 == 1 else 8 * 777, generator=g) * 1e-3).cuda()  # the second call grows the symmetric allocation
+    size = 8 * 777 if it % 2 == 0 else (n_values if it % 4 == 1 else 8 * 50000)  # the second call grows the symmetric allocation
+    grad = (torch.randn(size, generator=g) * 1e-3).cuda()
     a = via_nccl.all_reduce_mean(grad)
     b = via_peer.all_reduce_mean(grad)
     torch.cuda.synchronize()
     assert torch.equal(a, b), f"transports differ at call {it}"
+    c = chunked.all_reduce_mean(grad)
+    torch.cuda.synchronize()
+    assert torch.equal(a, c), f"chunked peer transport differs at call {it}"
+    if grad.numel() % 8 == 0:  # in place: the decode of a piece overwrites values whose encode has finished
+        inplace = grad.clone()
+        chunked.all_reduce_mean(inplace, out=inplace)
+        torch.cuda.synchronize()
+        assert torch.equal(a, inplace), f"in-place chunked exchange differs at call {it}"
 via_peer.check()
+chunked.check()
 dist.barrier()
 if rank == 0:
     print("PEER_OK")
