@@ -52,6 +52,8 @@ SIGNATURES = {
     "coset_d4_fake_quant_bwd": [_vp, _i32, _vp, _vp, _i64, _i64, _f32, _vp, _vp, _vp],
     "coset_lattice_babai": [_vp, _i64, _i32, _vp, _vp, _f32, _vp, _vp],
     "coset_e8_dequant_gemm": [_vp, _vp, _i64, _i32, _i32, _vp, _i64, _i32, _vp, _vp, _i64, _f32, _vp, _vp],
+    "coset_e8_decode_gemm_scratch_bytes": [_i32, _i32],
+    "coset_e8_decode_gemm": [_vp, _vp, _i64, _i32, _i32, _vp, _i64, _i32, _vp, _vp, _i32, _i64, _f32, _vp, _i64, _vp, _vp],
     "coset_layer_beta": [_vp, _vp, _vp, _i64, _vp, _vp],
     "coset_e8_layer_fake_quant_fwd": [_vp, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _i32, _vp, _vp, _vp],
     "coset_e8_layer_fake_quant_bwd": [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _vp, _vp],

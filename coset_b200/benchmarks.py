@@ -5,8 +5,8 @@ exist, pyproject.toml:67).  One JSON line per measurement:
     python -m coset_b200.benchmarks vlut       # code-domain matmul, W [4096, 4096], T in {1, 16, 256, 4096}
     python -m torch.distributed.run --nproc-per-node N -m coset_b200.benchmarks gradcomm
                                                # E8-quantised gradient exchange, BERT-base-shaped gradient
-    python -m coset_b200.benchmarks profile-gemv | profile-gemv16 | profile-gemm
-                                               # small fixed cases of the two matmul kernels for a profiler capture
+    python -m coset_b200.benchmarks profile-gemv | profile-gemv16 | profile-gemm | profile-gemm-pair
+                                               # small fixed cases of the matmul kernels for a profiler capture
 
 Timing: CUDA events on the current stream, warm-up first, inputs resident on the device.
 Roofline denominators: MEASURED_PEAKS.json at the repository root when present, else the
@@ -175,6 +175,16 @@ def iter_vlut(tilings=("block", "row")):
                        "tokens_per_s": T / (ms2 * 1e-3), "path": "fused tcgen05 dequant-GEMM (no dense weight in HBM)",
                        "timing": "CUDA graph replay", "bound": "tensor", "TFLOPs": flops / (ms2 * 1e-3) / 1e12,
                        "frac": flops / (ms2 * 1e-3) / 1e12 / tf, "peaks": src}
+                from .vlut import e8_decode_gemm
+                scratch = torch.empty(n * n, dtype=torch.bfloat16, device="cuda")
+                e8_decode_gemm(lin.codes, lin.beta, bpt, x, None, check=True, scratch=scratch)
+                ms3 = graph_time(lambda: e8_decode_gemm(lin.codes, lin.beta, bpt, x, None, scratch=scratch), calls=10, replays=5)
+                yield {"bench": "vlut_matmul", "tiling": tiling, "T": T, "shape": [n, n], "ms": ms3,
+                       "tokens_per_s": T / (ms3 * 1e-3),
+                       "path": "decode to a transient bf16 buffer + TMA-fed tcgen05 cta_group::2 GEMM (two launches, no dense weight kept)",
+                       "timing": "CUDA graph replay", "bound": "tensor", "TFLOPs": flops / (ms3 * 1e-3) / 1e12,
+                       "frac": flops / (ms3 * 1e-3) / 1e12 / tf, "peaks": src}
+                del scratch
 
 
 def bench_vlut():
@@ -324,8 +334,9 @@ def bench_gradcomm():
 def profile_case(which):
     """Small fixed cases for a profiler capture (W 4096 x 4096, per-block scales, bf16 tokens):
     `profile-gemv` / `profile-gemv16` run the few-token code-domain product five times at T = 1 / 16, `profile-gemm` the
-    fused tcgen05 dequant-GEMM three times at T = 2048 and checks its status word."""
-    from .vlut import E8CodeLinear, e8_dequant_gemm
+    fused tcgen05 dequant-GEMM three times at T = 2048 and checks its status word, `profile-gemm-pair` the same with
+    the decode + cta_group::2 GEMM."""
+    from .vlut import E8CodeLinear, e8_decode_gemm, e8_dequant_gemm
     torch.manual_seed(0)
     n = 4096
     W = (torch.randn(n, n) * 0.02).cuda()
@@ -337,8 +348,9 @@ def profile_case(which):
             lin(x)
     else:
         x = torch.randn(2048, n, device="cuda").to(torch.bfloat16)
+        gemm = e8_decode_gemm if which == "profile-gemm-pair" else e8_dequant_gemm
         for _ in range(3):
-            e8_dequant_gemm(lin.codes, lin.beta, 1, x, None, check=True)
+            gemm(lin.codes, lin.beta, 1, x, None, check=True)
     torch.cuda.synchronize()
     print("ok")
 
@@ -346,7 +358,7 @@ def profile_case(which):
 def main(argv=None):
     argv = sys.argv[1:] if argv is None else argv
     which = argv[0] if argv else "all"
-    if which in ("profile-gemv", "profile-gemv16", "profile-gemm"):
+    if which in ("profile-gemv", "profile-gemv16", "profile-gemm", "profile-gemm-pair"):
         profile_case(which)
         return
     if which in ("qat", "all"):

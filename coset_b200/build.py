@@ -25,6 +25,7 @@ SOURCES = [
     "e8_stats.cu",
     "e8_ref.cu",
     "e8_dequant_gemm.cu",
+    "e8_decode_gemm.cu",
     "d4.cu",
 ]
 

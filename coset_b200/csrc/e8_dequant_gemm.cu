@@ -25,15 +25,15 @@
 #include "common.cuh"
 #include "e8_fast.cuh"
 #include "e8_io.cuh"
+#include "umma.cuh"
 
 using namespace coset;
+using namespace coset::umma;
 
 namespace {
 
-constexpr int BM = 128, BK = 64;
 constexpr int PRODUCERS = 512;            // 16 warps decode / copy tiles and run the epilogue
 constexpr int THREADS = PRODUCERS + 32;   // + 1 warp whose first lane issues the MMAs
-constexpr int TILE_BYTES = BM * BK * 2;   // one 128 x 64 bf16 activation tile, 16 KiB
 constexpr uint32_t TMEM_COLS = 512;       // MSUB accumulators of BN fp32 columns = the whole tensor memory of the SM
 
 // CTA tile = (MSUB x 128 tokens) x BN output features over STAGES pipeline stages.  The shape in use is
@@ -59,89 +59,6 @@ struct GemmCfg {
     static_assert(STAGE_BYTES >= 16 * 32 * 33 * 4 || STAGES >= 2, "epilogue scratch");
 };
 using CfgWide = GemmCfg<4, 128, 2>;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-// Bounded wait: false if the phase did not complete within about 0.2 s (far beyond any healthy wait of this
-// kernel, whose whole run takes well under a millisecond per wave).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    uint64_t t0 = 0;
-    for (int it = 0; it < (1 << 24); ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((it & 63) == 63) {
-            uint64_t now;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > 200000000ull) return false;
-        }
-    }
-    return false;
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// Adds `bytes` to the transaction count the barrier's current phase waits for (no arrival).
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// TMA: one 64 (K) x 128 (tokens) bf16 box of x -> shared memory in the 128-byte swizzle; rows beyond
-// T are filled with zeros.  k0 * 2 bytes is a multiple of 128, so the 16-byte rule on the inner
-// coordinate holds.  No multicast: the box lands in this CTA only.
-__device__ __forceinline__ void tma_load_a(uint32_t dst, const CUtensorMap* map, int k0, int tok, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(k0), "r"(tok), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-// K-major, SWIZZLE_128B operand tile: start address, LBO = 1 (unused with swizzle), SBO = 1024 B
-// between 8-row groups, descriptor version 1 (sm_100), layout type 2 (128-byte swizzle).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-
-__device__ __forceinline__ uint64_t make_desc(uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; }
-
-__device__ __forceinline__ uint32_t swizzled_chunk_offset(int row, int chunk) {
-    return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
-}
-
-__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 template <int MODE, class Cfg>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -342,32 +259,6 @@ k_dequant_gemm(const uint32_t* __restrict__ codes, const float* __restrict__ bet
     }
 }
 
-// Tensor map of the activations x[T, K] (bf16, row stride ldx): boxes of 64 (K) x 128 (rows), 128-byte
-// swizzle, zero fill outside the tensor.  The driver entry point is looked up through the runtime so
-// that the library does not link against the driver library.
-int make_x_map(CUtensorMap* map, const void* x, int K, int T, int64_t ldx) {
-    typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static EncodeTiled encode = nullptr;
-    if (!encode) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (check_cuda(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres), "cudaGetDriverEntryPoint")) return COSET_E_STATE;
-        if (qres != cudaDriverEntryPointSuccess || !fn) return fail(COSET_E_STATE, "cuTensorMapEncodeTiled is not available in this driver");
-        encode = (EncodeTiled)fn;
-    }
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)T};
-    const cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};  // bytes between rows; a multiple of 16 (ldx % 8 == 0)
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
-    const cuuint32_t elem[2] = {1, 1};
-    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, elem,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(COSET_E_BADARG, "cuTensorMapEncodeTiled failed with code %d", (int)r);
-    return 0;
-}
-
 }  // namespace
 
 extern "C" int coset_e8_dequant_gemm(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
@@ -379,7 +270,7 @@ extern "C" int coset_e8_dequant_gemm(const void* codes, const float* beta, int64
     if (ldx < n_in || ldy < n_out || (ldx % 8) != 0) return fail(COSET_E_BADARG, "leading dimensions: ldx >= n_in and a multiple of 8, ldy >= n_out");
     if (!aligned(x_bf16, 16) || !aligned(codes, 4)) return fail(COSET_E_ALIGN, "x must be 16-byte and codes 4-byte aligned");
     CUtensorMap x_map;
-    if (int e = make_x_map(&x_map, x_bf16, n_in, T, ldx)) return e;
+    if (int e = make_bf16_map(&x_map, x_bf16, n_in, T, ldx)) return e;
     if (beta && blocks_per_tile < 1) return fail(COSET_E_BADARG, "blocks_per_tile must be >= 1");
     cudaStream_t st = (cudaStream_t)stream;
     const uint2* table = residual_table_q4(st);

@@ -76,23 +76,73 @@ def e8_dequant_gemm(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_pe
     return y
 
 
+def e8_decode_gemm(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_per_tile: int, x: torch.Tensor,
+                   bias: Optional[torch.Tensor] = None, check: bool = False, clip: float = 0.0,
+                   scratch: Optional[torch.Tensor] = None, out_dtype=torch.float32) -> torch.Tensor:
+    """The product of e8_dequant_gemm in two launches: the weight is decoded to bf16 into `scratch` (transient,
+    n_out * n_in bf16 values, allocated here when not given) and multiplied by a TMA-fed tcgen05 GEMM on pairs
+    of CTAs (cta_group::2).  Same bits as e8_dequant_gemm and, measured, the same speed up to 8192 tokens, a few
+    percent more beyond; nothing dense survives the call.  out_dtype: float32 or bfloat16 (rounded once from the
+    float32 accumulator)."""
+    if out_dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("out_dtype must be float32 or bfloat16")
+    _lib.require_cuda(codes, "codes")
+    _lib.require_cuda(x, "x")
+    if x.dtype != torch.bfloat16:
+        raise TypeError("e8_decode_gemm takes bfloat16 activations")
+    if codes.dtype != torch.int32 or codes.dim() != 2 or not codes.is_contiguous():
+        raise ValueError("codes must be a contiguous int32 tensor [n_out, n_in / 8]")
+    n_out, kb = codes.shape
+    if x.dim() != 2 or x.shape[1] != kb * 8 or (kb * 8) % 64:
+        raise ValueError(f"x must be [T, {kb * 8}] with n_in a multiple of 64, got {tuple(x.shape)}")
+    x = x.contiguous()
+    T = x.shape[0]
+    need = n_out * kb * 8
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.bfloat16, device=x.device)
+    elif scratch.dtype != torch.bfloat16 or scratch.numel() < need or not scratch.is_contiguous() or scratch.device != x.device:
+        raise ValueError(f"scratch must be a contiguous bfloat16 tensor of at least {need} values on {x.device}")
+    y = torch.empty((T, n_out), dtype=out_dtype, device=x.device)
+    status = torch.zeros(1, dtype=torch.int32, device=x.device)
+    b = beta.to(torch.float32).contiguous().view(-1) if beta is not None else None
+    bias32 = bias.to(torch.float32).contiguous() if bias is not None else None
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().coset_e8_decode_gemm(_lib.ptr(codes), _lib.ptr(b) if b is not None else None,
+                                             int(blocks_per_tile), n_out, kb * 8, _lib.ptr(x), x.stride(0), T,
+                                             _lib.ptr(bias32) if bias32 is not None else None, _lib.ptr(y),
+                                             _lib.dtype_code(y, "y"), y.stride(0), float(clip), _lib.ptr(scratch), scratch.numel() * 2,
+                                             _lib.ptr(status), _lib.stream())
+    _lib.check(rc, "coset_e8_decode_gemm")
+    if check and int(status.item()) != 0:
+        raise RuntimeError("coset_e8_decode_gemm: a barrier wait expired inside the kernel; the result is invalid")
+    return y
+
+
 class E8CodeLinear(nn.Module):
     """Linear layer that owns E8 codes + scales instead of a dense weight (inference only).
 
     Its state_dict is self-describing (codes, beta, bias, blocks_per_tile, weight_clip_value), so a
     layer can be rebuilt from a checkpoint alone with `E8CodeLinear.from_state_dict`.
+    More than small_t_max bf16 tokens go to (large_t_path): "tcgen05" -- this library's tensor-core kernels, which
+    keep no dense weight: decode to a transient bf16 buffer + TMA-fed cta_group::2 GEMM from 1024 tokens, the
+    single-launch fused kernel below; "cublas" -- a cached dense bf16 copy and the library GEMM; "auto" (default)
+    -- the own kernels from PAIR_GEMM_MIN_T tokens, the library path for the few hundred tokens in between, where
+    decoding the whole weight per call costs more than the product itself.
     weight_clip_value > 0: the weights are clamp(decode(codes) / beta, +-clip), the clamp the training
     layer applies after de-scaling (coset/core/layers.py:463); 0 disables it."""
 
+    PAIR_GEMM_MIN_T = 2048  # from here on the decode + cta_group::2 GEMM is within 10-25 % of the library on a dense copy
+
     def __init__(self, codes: torch.Tensor, beta: torch.Tensor, blocks_per_tile: int,
-                 bias: Optional[torch.Tensor] = None, small_t_max: int = 64, large_t_path: str = "cublas",
+                 bias: Optional[torch.Tensor] = None, small_t_max: int = 64, large_t_path: str = "auto",
                  weight_clip_value: float = 0.0):
         super().__init__()
         self.out_features, kb = codes.shape
         self.in_features = kb * 8
         self.small_t_max = small_t_max
-        if large_t_path not in ("cublas", "tcgen05"):
-            raise ValueError("large_t_path must be 'cublas' (dequantise once + library GEMM) or 'tcgen05' (fused kernel)")
+        if large_t_path not in ("auto", "cublas", "tcgen05"):
+            raise ValueError("large_t_path must be 'auto', 'cublas' (dequantise once, keep the dense copy, library GEMM) "
+                             "or 'tcgen05' (this library's tensor-core kernels only, no dense copy kept)")
         self.large_t_path = large_t_path
         self.register_buffer("codes", codes.contiguous())
         self.register_buffer("beta", beta.to(torch.float32).contiguous().view(-1))
@@ -170,8 +220,12 @@ class E8CodeLinear(nn.Module):
         else:
             if x2.dtype == torch.float32:
                 y = torch.nn.functional.linear(x2, self.dense_weight(torch.float32), self.bias)
-            elif self.large_t_path == "tcgen05" and x2.dtype == torch.bfloat16 and self.in_features % 64 == 0:
-                y = e8_dequant_gemm(self.codes, self.beta, self.blocks_per_tile, x2, self.bias, clip=clip).to(x2.dtype)
+            elif x2.dtype == torch.bfloat16 and self.in_features % 64 == 0 and (
+                    self.large_t_path == "tcgen05" or (self.large_t_path == "auto" and x2.shape[0] >= self.PAIR_GEMM_MIN_T)):
+                if x2.shape[0] >= 1024:
+                    y = e8_decode_gemm(self.codes, self.beta, self.blocks_per_tile, x2, self.bias, clip=clip, out_dtype=torch.bfloat16)
+                else:
+                    y = e8_dequant_gemm(self.codes, self.beta, self.blocks_per_tile, x2, self.bias, clip=clip).to(x2.dtype)
             else:
                 b = self.bias.to(x2.dtype) if self.bias is not None else None
                 y = torch.nn.functional.linear(x2, self._dense_bf16().to(x2.dtype), b)

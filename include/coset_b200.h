@@ -355,6 +355,23 @@ int coset_e8_dequant_gemm(const void* codes, const float* beta, int64_t blocks_p
                           const void* x_bf16, int64_t ldx, int T, const float* bias, float* y, int64_t ldy,
                           float clip /* as in coset_e8_vlut_gemv; 0 = none */, int* status, void* stream);
 
+/*
+ * The same product in two launches: decode the whole weight to bf16 into `scratch`, then a TMA-fed
+ * tcgen05 GEMM on pairs of CTAs (tcgen05.mma.cta_group::2, 256 x 256 x 16 per instruction).  The decode
+ * leaves the GEMM's K loop; measured speed equals the fused form's up to 8192 tokens and is a few percent
+ * higher beyond.  `scratch` is transient (rewritten
+ * by every call, nothing in it has to survive the call); it must hold
+ * coset_e8_decode_gemm_scratch_bytes(n_out, n_in) = 2 * n_out * n_in bytes and be 16-byte aligned.
+ * Arguments, result and tolerance as for coset_e8_dequant_gemm (the bf16 weights are the same bits);
+ * y: [T, ldy] float32 or bf16 (y_dtype), rounded once from the float32 accumulator plus bias.
+ * Replaces the dense-weight matmul after a one-off dequantisation, coset/legacy/quant/vlut.py:72-117
+ * (`vlut_mac_and_accumulate` over decoded rows); the reference has no tensor-core path.
+ */
+int64_t coset_e8_decode_gemm_scratch_bytes(int n_out, int n_in);
+int coset_e8_decode_gemm(const void* codes, const float* beta, int64_t blocks_per_tile, int n_out, int n_in,
+                         const void* x_bf16, int64_t ldx, int T, const float* bias, void* y, int y_dtype,
+                         int64_t ldy, float clip, void* scratch, int64_t scratch_bytes, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -147,7 +147,7 @@ def cfg4():
 
 @pytest.mark.parametrize("T", [1, 16, 256, 4096])
 def test_code_domain_product_at_config_shape(cfg4, T):
-    from coset_b200.vlut import E8CodeLinear, e8_dequant_gemm, e8_vlut_matmul
+    from coset_b200.vlut import E8CodeLinear, e8_decode_gemm, e8_dequant_gemm, e8_vlut_matmul
     lin = E8CodeLinear.from_weight(cfg4["W"].cuda(), cfg4["beta"].cuda(), 1)
     assert np.array_equal(lin.codes.cpu().numpy().view(np.uint32).reshape(-1), cfg4["codes"])
     torch.manual_seed(100 + T)
@@ -159,6 +159,10 @@ def test_code_domain_product_at_config_shape(cfg4, T):
     assert rel(got_layer.float().cpu().numpy(), want) < 1e-2
     got_gemm = e8_dequant_gemm(lin.codes, lin.beta, 1, xd, None, check=True)
     assert rel(got_gemm.cpu().numpy(), want) < 1e-2
+    got_pair = e8_decode_gemm(lin.codes, lin.beta, 1, xd, None, check=True)
+    assert rel(got_pair.cpu().numpy(), want) < 1e-2
+    # same bf16 weights, same K order inside a K step: the two tensor-core forms differ by accumulation order at most
+    assert rel(got_pair.cpu().numpy(), got_gemm.cpu().numpy()) < 1e-5
     if T <= 16:
         got_gemv = e8_vlut_matmul(lin.codes, lin.beta, 1, xd)
         assert rel(got_gemv.cpu().numpy(), want) < 1e-2

@@ -85,8 +85,8 @@ def test_export_from_trained_layer():
 @pytest.mark.parametrize("tiling", ["block", "row"])
 def test_weight_clip_in_every_kernel(tiling):
     """clamp(decode / beta, +-clip) with a clip that cuts about a third of the weights, against the CPU
-    restatement: few-token kernel (float32 and bf16 activations), library path and fused tcgen05 kernel."""
-    from coset_b200.vlut import E8CodeLinear, e8_dequant_gemm
+    restatement: few-token kernel (float32 and bf16 activations), library path and both tcgen05 forms."""
+    from coset_b200.vlut import E8CodeLinear, e8_decode_gemm, e8_dequant_gemm
     W, beta, bpt, digits, w_hat = make(256, 512, tiling)
     clip = 0.03
     w_clip = np.clip(w_hat, -clip, clip)
@@ -103,24 +103,53 @@ def test_weight_clip_in_every_kernel(tiling):
     assert rel(lin(xb.cuda()).float().cpu().numpy(), want) < 1e-2
     got = e8_dequant_gemm(lin.codes, lin.beta, bpt, xb.cuda(), lin.bias, check=True, clip=clip)
     assert rel(got.cpu().numpy(), want) < 1e-2
+    got2 = e8_decode_gemm(lin.codes, lin.beta, bpt, xb.cuda(), lin.bias, check=True, clip=clip)
+    assert rel(got2.cpu().numpy(), want) < 1e-2
 
 
+@pytest.mark.parametrize("form", ["fused", "decode_then_pair_gemm"])
 @pytest.mark.parametrize("T,n_out,n_in,tiling", [(128, 128, 64, "block"), (256, 256, 512, "block"), (300, 200, 1024, "row"), (1100, 384, 256, "block"),
-                                                  (1, 128, 128, "block")])
-def test_tcgen05_dequant_gemm(T, n_out, n_in, tiling):
-    """Fused decode + tensor-core product against decode-then-float32-matmul of the CPU restatement."""
-    from coset_b200.vlut import E8CodeLinear, e8_dequant_gemm
+                                                  (1, 128, 128, "block"), (513, 640, 512, "row")])
+def test_tcgen05_dequant_gemm(T, n_out, n_in, tiling, form):
+    """Both tensor-core forms (decode fused into the K loop; decode to a transient bf16 buffer followed by the
+    cta_group::2 GEMM) against decode-then-float32-matmul of the CPU restatement.  Shapes: ragged token counts,
+    feature counts that are not multiples of a tile (200, 384, 640), one K step and sixteen."""
+    from coset_b200.vlut import E8CodeLinear, e8_decode_gemm, e8_dequant_gemm
+    gemm = e8_dequant_gemm if form == "fused" else e8_decode_gemm
     W, beta, bpt, digits, w_hat = make(n_out, n_in, tiling, seed=T)
     bias = torch.randn(n_out)
     lin = E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt, bias.cuda())
     x = torch.randn(T, n_in).to(torch.bfloat16)
-    got = e8_dequant_gemm(lin.codes, lin.beta, bpt, x.cuda(), lin.bias, check=True).cpu().numpy()
+    got = gemm(lin.codes, lin.beta, bpt, x.cuda(), lin.bias, check=True).cpu().numpy()
     want = x.float().numpy().astype(np.float64) @ w_hat.astype(np.float64).T + bias.double().numpy()
     assert rel(got, want) < 1e-2
     # against the same product with bf16-rounded weights the kernel should agree to fp32 accumulation error
     w_bf = torch.from_numpy(w_hat).to(torch.bfloat16).double().numpy()
     want_bf = x.double().numpy() @ w_bf.T + bias.double().numpy()
     assert rel(got, want_bf) < 2e-3  # weights may differ from the exactly divided ones by one bf16 ulp
+    if form != "fused":  # bf16 result: the same float32 accumulator plus bias, rounded once by the kernel
+        got16 = gemm(lin.codes, lin.beta, bpt, x.cuda(), lin.bias, check=True, out_dtype=torch.bfloat16)
+        assert got16.dtype == torch.bfloat16
+        assert torch.equal(got16.cpu(), torch.from_numpy(got).to(torch.bfloat16))
+
+
+def test_decode_gemm_scratch_is_checked_and_reusable():
+    """The transient weight buffer: refused when too small or of the wrong type; one buffer serves layers of
+    different shapes one after the other (nothing in it survives a call)."""
+    from coset_b200.vlut import E8CodeLinear, e8_decode_gemm
+    scratch = torch.empty(512 * 256, dtype=torch.bfloat16, device="cuda")
+    for n_out, n_in in ((512, 256), (128, 192), (256, 512)):
+        W, beta, bpt, digits, w_hat = make(n_out, n_in, "block", seed=n_out)
+        lin = E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt)
+        x = torch.randn(70, n_in).to(torch.bfloat16)
+        got = e8_decode_gemm(lin.codes, lin.beta, bpt, x.cuda(), None, check=True, scratch=scratch).cpu().numpy()
+        assert rel(got, x.float().numpy().astype(np.float64) @ w_hat.astype(np.float64).T) < 1e-2
+    with pytest.raises(ValueError):
+        e8_decode_gemm(lin.codes, lin.beta, bpt, x.cuda(), None, scratch=scratch[:100])
+    with pytest.raises(ValueError):
+        e8_decode_gemm(lin.codes, lin.beta, bpt, x.cuda(), None, scratch=scratch.float())
+    from coset_b200 import _lib
+    assert _lib.lib().coset_e8_decode_gemm_scratch_bytes(256, 512) == 256 * 512 * 2
 
 
 SHARD_WORKER = r'''
