@@ -158,7 +158,10 @@ def iter_vlut(tilings=("block", "row")):
             ms = graph_time(lambda: lin(x)) if T <= 256 else cuda_time(lambda: lin(x), iters=10)
             flops = 2.0 * T * n * n
             rec = {"bench": "vlut_matmul", "tiling": tiling, "T": T, "shape": [n, n], "ms": ms,
-                   "tokens_per_s": T / (ms * 1e-3), "path": "code-domain kernel" if T <= 64 else "bf16 dequant + tensor cores",
+                   "tokens_per_s": T / (ms * 1e-3),
+                   "path": ("E8CodeLinear default: code-domain kernel" if T <= 64 else
+                            "E8CodeLinear default: cached dense bf16 copy + library GEMM" if T < lin.PAIR_GEMM_MIN_T else
+                            "E8CodeLinear default: decode + tcgen05 cta_group::2 GEMM, bf16 result"),
                    "timing": "CUDA graph replay" if T <= 256 else "CUDA events over eager calls",
                    "peaks": src}
             if T <= 64:
@@ -167,6 +170,12 @@ def iter_vlut(tilings=("block", "row")):
             else:
                 rec.update({"bound": "tensor", "TFLOPs": flops / (ms * 1e-3) / 1e12, "frac": flops / (ms * 1e-3) / 1e12 / tf})
             yield rec
+            if T >= lin.PAIR_GEMM_MIN_T:  # the library path beside it
+                dense = lin._dense_bf16()
+                msl = cuda_time(lambda: torch.nn.functional.linear(x, dense), iters=10)
+                yield {"bench": "vlut_matmul", "tiling": tiling, "T": T, "shape": [n, n], "ms": msl, "tokens_per_s": T / (msl * 1e-3),
+                       "path": "library GEMM on a cached dense bf16 copy (large_t_path='cublas')", "timing": "CUDA events over eager calls",
+                       "bound": "tensor", "TFLOPs": flops / (msl * 1e-3) / 1e12, "frac": flops / (msl * 1e-3) / 1e12 / tf, "peaks": src}
             if T > 64:
                 from .vlut import e8_dequant_gemm
                 e8_dequant_gemm(lin.codes, lin.beta, bpt, x, None, check=True)
