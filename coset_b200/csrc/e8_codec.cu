@@ -550,7 +550,7 @@ static_assert(kDeferLists == kThreads, "the fix-up kernel scans one counter per 
 
 // Four blocks per thread (kThreads apart, so every access stays coalesced): all codes are
 // loaded before the first table lookup, which multiplies the gathers in flight per thread
-// (measured: 1 block 0.252 ms, 2 blocks 0.236 ms, 4 blocks 0.231 ms, 8 blocks 0.231 ms per 2^25 blocks).
+// (measured per 2^25 blocks: 2 per thread 0.236 ms, 4 per thread 0.231 ms, 8 per thread 0.231 ms).
 constexpr int kDecPerThread = 4;
 // TABLE is `uint2` (8-byte entries) or `uint32_t` (packed 4-byte entries, used for float32 output,
 // where the kernel is bound by the gathers and not by instruction issue).
