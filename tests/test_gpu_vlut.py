@@ -133,6 +133,25 @@ def test_tcgen05_dequant_gemm(T, n_out, n_in, tiling, form):
         assert torch.equal(got16.cpu(), torch.from_numpy(got).to(torch.bfloat16))
 
 
+@pytest.mark.parametrize("path", ["auto", "tcgen05", "cublas"])
+def test_layer_dispatch_for_many_tokens(path):
+    """Every large_t_path of E8CodeLinear at token counts on both sides of its thresholds (64 / 1024 / 2048):
+    same product within the bf16 tolerance, result in the activations' type; 'tcgen05' keeps no dense copy."""
+    from coset_b200.vlut import E8CodeLinear
+    W, beta, bpt, digits, w_hat = make(256, 512, "row", seed=5)
+    bias = torch.randn(256)
+    lin = E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt, bias.cuda(), large_t_path=path)
+    for T in (65, 300, 1024, 1100, 2048, 2100):
+        x = torch.randn(T, 512).to(torch.bfloat16)
+        got = lin(x.cuda())
+        assert got.dtype == torch.bfloat16 and tuple(got.shape) == (T, 256)
+        want = x.float().numpy().astype(np.float64) @ w_hat.astype(np.float64).T + bias.double().numpy()
+        assert rel(got.float().cpu().numpy(), want) < 1e-2, (path, T)
+    assert (lin._dense is None) == (path == "tcgen05")
+    with pytest.raises(ValueError):
+        E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt, large_t_path="fastest")
+
+
 def test_decode_gemm_scratch_is_checked_and_reusable():
     """The transient weight buffer: refused when too small or of the wrong type; one buffer serves layers of
     different shapes one after the other (nothing in it survives a call)."""
