@@ -556,7 +556,7 @@ def main():
         line.update({
             "value": value,
             "ms_per_step": total_ms / args.steps,
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": 3 * args.steps,  # per step: k_encode_q4m2_main, k_encode_q4m2_fix, k_decode_q4m2
             "frac_of_hbm_peak": value / world / peak,
             "roofline": {"bound": "hbm", "kernel": "encode pass = k_encode_q4m2_main + its fix-up launch k_encode_q4m2_fix (dominant: %.0f%% of the step)" % (100 * per[0] / (per[0] + per[1])),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
