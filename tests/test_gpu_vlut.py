@@ -152,6 +152,46 @@ def test_layer_dispatch_for_many_tokens(path):
         E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt, large_t_path="fastest")
 
 
+def test_decode_gemm_through_the_c_abi_with_strides_and_without_scales():
+    """coset_e8_decode_gemm called as a foreign runtime would: raw pointers, activation rows and result rows
+    with padding between them (ldx > n_in, ldy > n_out), no scales (beta = NULL: weights are the plain
+    reconstructions), no bias; and the empty shapes return at once."""
+    from coset_b200 import _lib
+    L = _lib.lib()
+    torch.manual_seed(3)
+    n_out, n_in, T = 200, 192, 333
+    W = torch.randn(n_out, n_in) * 0.6
+    digits = O.encode(W.numpy().reshape(-1, 8), threads=8)
+    w_hat = O.decode(digits, threads=8).reshape(n_out, n_in)
+    codes = torch.from_numpy(O.pack_q4(digits).view(np.int32).reshape(n_out, n_in // 8)).cuda()
+    ldx, ldy = n_in + 16, n_out + 5
+    xbuf = torch.zeros(T, ldx, dtype=torch.bfloat16, device="cuda")
+    x = torch.randn(T, n_in).to(torch.bfloat16)
+    xbuf[:, :n_in] = x.cuda()
+    ybuf = torch.full((T, ldy), 7.0, dtype=torch.float32, device="cuda")
+    scratch = torch.empty(n_out * n_in, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = L.coset_e8_decode_gemm(_lib.ptr(codes), None, 1, n_out, n_in, _lib.ptr(xbuf), ldx, T, None, _lib.ptr(ybuf), _lib.DTYPE_F32, ldy,
+                                0.0, _lib.ptr(scratch), scratch.numel() * 2, _lib.ptr(status), _lib.stream())
+    assert rc == 0, L.coset_last_error_string()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    want = x.float().numpy().astype(np.float64) @ w_hat.astype(np.float64).T
+    assert rel(ybuf[:, :n_out].cpu().numpy(), want) < 1e-2
+    assert bool((ybuf[:, n_out:] == 7.0).all())  # the padding between result rows is untouched
+    assert torch.equal(scratch.view(n_out, n_in).float().cpu(), torch.from_numpy(w_hat).to(torch.bfloat16).float())  # exact: halves of small integers
+    for shape in ((0, n_in, T), (n_out, n_in, 0)):
+        assert L.coset_e8_decode_gemm(_lib.ptr(codes), None, 1, shape[0], shape[1], _lib.ptr(xbuf), ldx, shape[2], None, _lib.ptr(ybuf),
+                                      _lib.DTYPE_F32, ldy, 0.0, _lib.ptr(scratch), scratch.numel() * 2, None, _lib.stream()) == 0
+    # refused: scratch too small, n_in not a multiple of 64, unknown result type
+    assert L.coset_e8_decode_gemm(_lib.ptr(codes), None, 1, n_out, n_in, _lib.ptr(xbuf), ldx, T, None, _lib.ptr(ybuf), _lib.DTYPE_F32, ldy,
+                                  0.0, _lib.ptr(scratch), 16, None, _lib.stream()) < 0
+    assert L.coset_e8_decode_gemm(_lib.ptr(codes), None, 1, n_out, 100, _lib.ptr(xbuf), ldx, T, None, _lib.ptr(ybuf), _lib.DTYPE_F32, ldy,
+                                  0.0, _lib.ptr(scratch), scratch.numel() * 2, None, _lib.stream()) < 0
+    assert L.coset_e8_decode_gemm(_lib.ptr(codes), None, 1, n_out, n_in, _lib.ptr(xbuf), ldx, T, None, _lib.ptr(ybuf), 9, ldy,
+                                  0.0, _lib.ptr(scratch), scratch.numel() * 2, None, _lib.stream()) < 0
+
+
 def test_decode_gemm_scratch_is_checked_and_reusable():
     """The transient weight buffer: refused when too small or of the wrong type; one buffer serves layers of
     different shapes one after the other (nothing in it survives a call)."""
