@@ -73,7 +73,8 @@ class E8GradientExchange:
     timeout_ms: bound of the cross-rank wait of the peer-memory transport (see coset_b200.peer).
     chunks: the peer-memory transport can cut a large gradient into this many pieces and decode piece k (NVLink
     reads, on a high-priority side stream) while piece k+1 is being encoded.  Default 1 = one piece: on 4 B200s
-    the 109.5 M-value gradient takes 0.460 / 0.491 / 0.544 / 0.665 ms with 1 / 2 / 4 / 8 pieces -- encoder and
+    the 109.5 M-value gradient takes 0.460 / 0.491 / 0.544 / 0.665 ms with 1 / 2 / 4 / 8 pieces (on 8: 0.767 / 0.797 /
+    0.856 / 0.963 ms) -- encoder and
     decoder both want every SM, so running them side by side moves no work off the critical path, while each
     extra piece adds an arrival (a cross-GPU round trip) and three launches.
     """
