@@ -138,23 +138,32 @@ class E8GradientExchange:
         if self.transport == "peer" and world > 1:
             self._all_reduce_mean_peer(padded, n_blocks, world, res)
         else:
-            codes, gathered = self._buffers(n_blocks, world, flat.device)
-            self._mark()
-            self.codec.encode(padded.view(n_blocks, 8), self.scale, codes)
-            self._mark()
-            if world > 1:
-                dist.all_gather_into_tensor(gathered.view(-1), codes, group=self.group)
-            else:
-                gathered.view(-1).copy_(codes)
-            self._mark()
-            self.codec.decode_mean(gathered, world, n_blocks, self.scale, res)
-            self._mark()
+            self._all_reduce_mean_gathered(padded, n_blocks, world, res)
         if direct:
             return out
         res = res.view(-1)[:n_values]
         if out is not None:
             out.copy_(res)
             return out
+        return res
+
+    def _all_reduce_mean_gathered(self, padded, n_blocks, world, res):
+        """Encode, all-gather the packed codes, decode-and-average, one after the other on the caller's stream.
+        (Pipelining the three over pieces of the gradient -- all-gather of piece k on a second stream beside the
+        encode of piece k+1 and the decode of piece k-1 -- was measured on 8 B200s at 1.126 / 1.196 / 1.106 /
+        1.177 / 1.437 ms for 1 / 2 / 3 / 4 / 8 pieces: the collective's own kernels and ours compete for the
+        same SMs, so nothing is gained and the form stays sequential.)"""
+        codes, gathered = self._buffers(n_blocks, world, padded.device)
+        self._mark()
+        self.codec.encode(padded.view(n_blocks, 8), self.scale, codes)
+        self._mark()
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), codes, group=self.group)
+        else:
+            gathered.view(-1).copy_(codes)
+        self._mark()
+        self.codec.decode_mean(gathered, world, n_blocks, self.scale, res)
+        self._mark()
         return res
 
     def overloaded_fraction(self, flat: torch.Tensor) -> float:
