@@ -46,7 +46,8 @@ def e8_vlut_matmul(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_per
 
 
 def e8_dequant_gemm(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_per_tile: int, x: torch.Tensor,
-                    bias: Optional[torch.Tensor] = None, check: bool = False, clip: float = 0.0) -> torch.Tensor:
+                    bias: Optional[torch.Tensor] = None, check: bool = False, clip: float = 0.0,
+                    status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Same product as e8_vlut_matmul for many tokens, on the tcgen05 tensor cores: weight tiles are
     decoded to bf16 in shared memory and never written to HBM.  x: bf16 [T, n_in], n_in % 64 == 0.
     check=True synchronises and raises if a bounded barrier wait expired inside the kernel."""
@@ -62,7 +63,8 @@ def e8_dequant_gemm(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_pe
     x = x.contiguous()
     T = x.shape[0]
     y = torch.empty((T, n_out), dtype=torch.float32, device=x.device)
-    status = torch.zeros(1, dtype=torch.int32, device=x.device)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=x.device)
     b = beta.to(torch.float32).contiguous().view(-1) if beta is not None else None
     bias32 = bias.to(torch.float32).contiguous() if bias is not None else None
     with torch.cuda.device(x.device):
@@ -78,7 +80,8 @@ def e8_dequant_gemm(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_pe
 
 def e8_decode_gemm(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_per_tile: int, x: torch.Tensor,
                    bias: Optional[torch.Tensor] = None, check: bool = False, clip: float = 0.0,
-                   scratch: Optional[torch.Tensor] = None, out_dtype=torch.float32) -> torch.Tensor:
+                   scratch: Optional[torch.Tensor] = None, out_dtype=torch.float32,
+                   status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The product of e8_dequant_gemm in two launches: the weight is decoded to bf16 into `scratch` (transient,
     n_out * n_in bf16 values, allocated here when not given) and multiplied by a TMA-fed tcgen05 GEMM on pairs
     of CTAs (cta_group::2).  Same bits as e8_dequant_gemm and, measured, the same speed up to 8192 tokens, a few
@@ -103,7 +106,8 @@ def e8_decode_gemm(codes: torch.Tensor, beta: Optional[torch.Tensor], blocks_per
     elif scratch.dtype != torch.bfloat16 or scratch.numel() < need or not scratch.is_contiguous() or scratch.device != x.device:
         raise ValueError(f"scratch must be a contiguous bfloat16 tensor of at least {need} values on {x.device}")
     y = torch.empty((T, n_out), dtype=out_dtype, device=x.device)
-    status = torch.zeros(1, dtype=torch.int32, device=x.device)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=x.device)
     b = beta.to(torch.float32).contiguous().view(-1) if beta is not None else None
     bias32 = bias.to(torch.float32).contiguous() if bias is not None else None
     with torch.cuda.device(x.device):
@@ -152,6 +156,7 @@ class E8CodeLinear(nn.Module):
         self.blocks_per_tile = int(blocks_per_tile)
         self.weight_clip_value = float(weight_clip_value)
         self._dense, self._dense_key = None, None  # bf16 copy for the library GEMM, rebuilt when codes / scales change
+        self._status = None                         # device word the tensor-core kernels set when a bounded wait gave up
 
     def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
         super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
@@ -209,6 +214,13 @@ class E8CodeLinear(nn.Module):
             self._dense, self._dense_key = self.dense_weight(torch.bfloat16), key
         return self._dense
 
+    def check(self):
+        """Synchronises and raises if a bounded barrier wait expired inside one of the tensor-core kernels since
+        the last check (their results are then invalid).  The kernels never hang: they give up after 0.2 s."""
+        if self._status is not None and int(self._status.item()) != 0:
+            self._status.zero_()
+            raise RuntimeError("E8CodeLinear: a barrier wait expired inside a tensor-core kernel; results since the last check are invalid")
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.in_features)
@@ -222,10 +234,14 @@ class E8CodeLinear(nn.Module):
                 y = torch.nn.functional.linear(x2, self.dense_weight(torch.float32), self.bias)
             elif x2.dtype == torch.bfloat16 and self.in_features % 64 == 0 and (
                     self.large_t_path == "tcgen05" or (self.large_t_path == "auto" and x2.shape[0] >= self.PAIR_GEMM_MIN_T)):
+                if self._status is None or self._status.device != x2.device:
+                    self._status = torch.zeros(1, dtype=torch.int32, device=x2.device)
                 if x2.shape[0] >= 1024:
-                    y = e8_decode_gemm(self.codes, self.beta, self.blocks_per_tile, x2, self.bias, clip=clip, out_dtype=torch.bfloat16)
+                    y = e8_decode_gemm(self.codes, self.beta, self.blocks_per_tile, x2, self.bias, clip=clip, out_dtype=torch.bfloat16,
+                                       status=self._status)
                 else:
-                    y = e8_dequant_gemm(self.codes, self.beta, self.blocks_per_tile, x2, self.bias, clip=clip).to(x2.dtype)
+                    y = e8_dequant_gemm(self.codes, self.beta, self.blocks_per_tile, x2, self.bias, clip=clip,
+                                        status=self._status).to(x2.dtype)
             else:
                 b = self.bias.to(x2.dtype) if self.bias is not None else None
                 y = torch.nn.functional.linear(x2, self._dense_bf16().to(x2.dtype), b)
@@ -328,7 +344,9 @@ class ColumnParallelE8CodeLinear(nn.Module):
         return mine.view(T, self.out_features).clone()
 
     def check(self):
-        """Raises if a bounded cross-rank wait of the peer-store path gave up (synchronises)."""
+        """Raises if a bounded cross-rank wait of the peer-store path, or a bounded barrier wait inside a
+        tensor-core kernel of the local product, gave up (synchronises)."""
+        self.local.check()
         if self._region is not None:
             self._region.check()
 

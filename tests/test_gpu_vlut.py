@@ -148,6 +148,12 @@ def test_layer_dispatch_for_many_tokens(path):
         want = x.float().numpy().astype(np.float64) @ w_hat.astype(np.float64).T + bias.double().numpy()
         assert rel(got.float().cpu().numpy(), want) < 1e-2, (path, T)
     assert (lin._dense is None) == (path == "tcgen05")
+    lin.check()  # no bounded wait gave up in any of the tensor-core kernels above
+    if path != "cublas":
+        lin._status.fill_(1)  # what a kernel whose wait expired leaves behind
+        with pytest.raises(RuntimeError):
+            lin.check()
+        lin.check()  # reported once, then clear
     with pytest.raises(ValueError):
         E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt, large_t_path="fastest")
 
