@@ -1,12 +1,13 @@
 """Inference with weights kept as E8 codes: E8CodeLinear.
 
 The weight of a trained HNLQLinearQAT layer is exported as packed q=4, M=2 codes (4 bytes per 8
-weights) plus the scales beta, and applied without ever storing a dense copy:
+weights) plus the scales beta, and applied from the codes:
 
-  * few tokens  (T <= small_t_max): the code-domain kernel coset_e8_vlut_gemv, bound by the code
+  * few tokens  (T <= small_t_max): the code-domain kernels of coset_e8_vlut_gemv, which read the code
     stream (8.4 - 16.8 MB for a 4096 x 4096 weight instead of 64 MB of float32);
-  * many tokens: the weight is dequantised once into bf16 by the decode kernel and multiplied on
-    the tensor cores.
+  * many tokens (from 2048 by default): the weight is decoded into a transient bf16 buffer and multiplied by
+    this library's tcgen05 GEMM (coset_e8_decode_gemm); nothing dense survives the call;
+  * in between, by default, the library GEMM on a cached dense bf16 copy (`large_t_path` chooses).
 
 The math is the reference's one-sided vLUT inner product (coset/legacy/quant/vlut.py:72-117) in
 the layer's scale convention W_q = decode(codes) / beta (coset/core/layers.py:453-460).
@@ -127,27 +128,30 @@ class E8CodeLinear(nn.Module):
 
     Its state_dict is self-describing (codes, beta, bias, blocks_per_tile, weight_clip_value), so a
     layer can be rebuilt from a checkpoint alone with `E8CodeLinear.from_state_dict`.
-    More than small_t_max bf16 tokens go to (large_t_path): "tcgen05" -- this library's tensor-core kernels, which
-    keep no dense weight: decode to a transient bf16 buffer + TMA-fed cta_group::2 GEMM from 1024 tokens, the
-    single-launch fused kernel below; "cublas" -- a cached dense bf16 copy and the library GEMM; "auto" (default)
-    -- the own kernels from PAIR_GEMM_MIN_T tokens, the library path for the few hundred tokens in between, where
-    decoding the whole weight per call costs more than the product itself.
+    Up to small_t_max tokens go to the code-domain kernels; more bf16 tokens go to (large_t_path): "tcgen05" --
+    this library's tensor-core kernels, which keep no dense weight: decode to a transient bf16 buffer + TMA-fed
+    cta_group::2 GEMM from 1024 tokens, the single-launch fused kernel below; "cublas" -- a cached dense bf16 copy
+    and the library GEMM; "auto" (default) -- the own kernels from PAIR_GEMM_MIN_T tokens, the library path for
+    the tokens in between, where decoding the whole weight per call costs more than the product itself.
+    small_t_max defaults to 16 ("auto", "cublas") or 48 ("tcgen05"): measured on a 4096 x 4096 layer the
+    code-domain kernels take 9.7 / 23 / 44 / 86 us for 1 / 16 / 32 / 64 tokens (they re-read and re-decode the
+    codes for every 16 tokens), the library on the cached copy 7-13 us, the fused kernel 64 us.
     weight_clip_value > 0: the weights are clamp(decode(codes) / beta, +-clip), the clamp the training
     layer applies after de-scaling (coset/core/layers.py:463); 0 disables it."""
 
     PAIR_GEMM_MIN_T = 2048  # from here on the decode + cta_group::2 GEMM is within 10-25 % of the library on a dense copy
 
     def __init__(self, codes: torch.Tensor, beta: torch.Tensor, blocks_per_tile: int,
-                 bias: Optional[torch.Tensor] = None, small_t_max: int = 64, large_t_path: str = "auto",
+                 bias: Optional[torch.Tensor] = None, small_t_max: Optional[int] = None, large_t_path: str = "auto",
                  weight_clip_value: float = 0.0):
         super().__init__()
         self.out_features, kb = codes.shape
         self.in_features = kb * 8
-        self.small_t_max = small_t_max
         if large_t_path not in ("auto", "cublas", "tcgen05"):
             raise ValueError("large_t_path must be 'auto', 'cublas' (dequantise once, keep the dense copy, library GEMM) "
                              "or 'tcgen05' (this library's tensor-core kernels only, no dense copy kept)")
         self.large_t_path = large_t_path
+        self.small_t_max = int(small_t_max) if small_t_max is not None else (48 if large_t_path == "tcgen05" else 16)
         self.register_buffer("codes", codes.contiguous())
         self.register_buffer("beta", beta.to(torch.float32).contiguous().view(-1))
         self.register_buffer("bias", bias.detach().clone() if bias is not None else None)

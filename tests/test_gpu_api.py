@@ -127,7 +127,7 @@ def test_packed_export_round_trip_with_default_clip(tiling):
     ex = layer.export_quantized(packed=True)
     assert ex["codes"].dtype == torch.int32 and tuple(ex["codes"].shape) == (64, 16)
     assert ex["metadata"]["weight_clip_value"] == 2.0 and ex["blocks_per_tile"] == (16 if tiling == "row" else 1)
-    lin = E8CodeLinear.from_exported(ex)
+    lin = E8CodeLinear.from_exported(ex, small_t_max=64)
     with torch.no_grad():
         wq = layer._quantize_weights()
         assert float((wq.abs() == 2.0).float().mean()) > 0.2  # the clamp really is active

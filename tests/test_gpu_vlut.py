@@ -37,7 +37,7 @@ def test_small_t_fp32_activations(tiling, T):
     from coset_b200.vlut import E8CodeLinear
     W, beta, bpt, digits, w_hat = make(256, 512, tiling)
     bias = torch.randn(256)
-    lin = E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt, bias.cuda())
+    lin = E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt, bias.cuda(), small_t_max=64)  # every T below: code-domain kernels
     assert np.array_equal(lin.codes.cpu().numpy().view(np.uint32).reshape(-1), O.pack_q4(digits))
     assert np.array_equal(lin.dense_weight().cpu().numpy(), w_hat)  # bit-exact dequantised weight
     x = torch.randn(T, 512)
@@ -92,7 +92,7 @@ def test_weight_clip_in_every_kernel(tiling):
     w_clip = np.clip(w_hat, -clip, clip)
     assert 0.1 < (np.abs(w_hat) > clip).mean() < 0.6
     bias = torch.randn(256)
-    lin = E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt, bias.cuda(), weight_clip_value=clip)
+    lin = E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt, bias.cuda(), weight_clip_value=clip, small_t_max=64)
     assert np.array_equal(lin.dense_weight().cpu().numpy(), w_clip)
     for T in (1, 3, 16, 40):
         x = torch.randn(T, 512)
@@ -141,7 +141,8 @@ def test_layer_dispatch_for_many_tokens(path):
     W, beta, bpt, digits, w_hat = make(256, 512, "row", seed=5)
     bias = torch.randn(256)
     lin = E8CodeLinear.from_weight(W.cuda(), beta.cuda(), bpt, bias.cuda(), large_t_path=path)
-    for T in (65, 300, 1024, 1100, 2048, 2100):
+    assert lin.small_t_max == (48 if path == "tcgen05" else 16)
+    for T in (16, 17, 48, 49, 65, 300, 1024, 1100, 2048, 2100):
         x = torch.randn(T, 512).to(torch.bfloat16)
         got = lin(x.cuda())
         assert got.dtype == torch.bfloat16 and tuple(got.shape) == (T, 256)
