@@ -291,6 +291,9 @@ __device__ __forceinline__ void biased_bytes_q4m2(uint32_t e0, uint32_t e1, uint
     odd = 2u * s_odd + rep;
 }
 
+// Twice the reconstruction from the two packed entries of a code, already loaded.
+__device__ __forceinline__ void twice_from_packed(uint32_t e0, uint32_t e1, float (&v2)[8]);
+
 __device__ __forceinline__ void decode_q4m2_twice(uint32_t code, const uint32_t* __restrict__ packed, float (&v2)[8]) {
     const uint32_t w0 = code & 0xffffu, w1 = code >> 16;
     // The residual of an all-zero level word is the zero vector, and the top level of a quantiser that is
@@ -298,6 +301,10 @@ __device__ __forceinline__ void decode_q4m2_twice(uint32_t code, const uint32_t*
     uint32_t e0 = kPackedZeroEntry, e1 = kPackedZeroEntry;
     if (w0) e0 = __ldg(packed + w0);
     if (w1) e1 = __ldg(packed + w1);
+    twice_from_packed(e0, e1, v2);
+}
+
+__device__ __forceinline__ void twice_from_packed(uint32_t e0, uint32_t e1, float (&v2)[8]) {
     uint32_t even, odd;
     biased_bytes_q4m2(e0, e1, even, odd);
     const float kOff = 12582912.0f + 5.0f * kNibbleBias, kOff7 = 12582912.0f + 5.0f * kNibbleBias7;
